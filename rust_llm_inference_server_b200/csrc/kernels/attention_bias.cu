@@ -7,6 +7,12 @@
 //   score(i, j) = scale * q_h(i) . k_g(j) + bias[min(i - j, n_dist - 1), h],  j <= i (and i - j < window)
 //   out_h(i) = sigmoid(gate_h(i)) * sum_j softmax_j(score) v_g(j)
 //
+// Options that other designs use, each off unless its argument is given: the first `rot_dims` entries of every
+// query and key head are rotated before the norm, entry 2i with entry 2i+1 by the angle position * inv_freq[i]
+// (cos and sin times `rot_mag`); queries are multiplied, after their norm, by 1 + coef * ln(floor((p + 1) /
+// every) + 1) at position p; slope_h * (i - j) is subtracted from a score; exp(sink_h) joins the softmax's
+// denominator (a term without key or value).  Values that are the keys as projected are had by v_off = k_off.
+//
 // `bias` is a float32 table [n_dist, n_heads] by distance (the host turns bucket rules into it; all
 // distances from n_dist - 1 on share the last row).  Norms, scores, softmax, value sums, the mixing and
 // the gate are float32 whatever the element type.
@@ -29,7 +35,9 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_kernel(
     const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
     const T* __restrict__ v_other, long long v_other_stride, float lambda,
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots,
-    int n_units, int nh, int nkv, int d, int dv, int page_size) {
+    int n_units, int nh, int nkv, int d, int dv, int page_size,
+    const float* __restrict__ inv_freq, int rot_dims, float rot_mag, const int* __restrict__ positions,
+    float q_temp_coef, int q_temp_every) {
     pdl_wait_and_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int unit = blockIdx.x * WARPS + warp;
@@ -46,10 +54,29 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_kernel(
     for (int i = 0; i < MAX_D / 32; ++i) {
         const int c = lane + 32 * i;
         v[i] = c < d ? to_f<T>(x[c]) : 0.f;
-        ss = fmaf(v[i], v[i], ss);
     }
+    const int pos = positions != nullptr ? positions[t] : 0;
+    if (rot_dims > 0) {
+        // lanes 2j and 2j+1 hold a pair (32 i is even)
+#pragma unroll
+        for (int i = 0; i < MAX_D / 32; ++i) {
+            const int c = lane + 32 * i;
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
+            if (c < rot_dims) {
+                float sn, cs;
+                sincosf((float)pos * inv_freq[c >> 1], &sn, &cs);
+                sn *= rot_mag;
+                cs *= rot_mag;
+                v[i] = (c & 1) ? rope_second(other, v[i], cs, sn) : rope_first(v[i], other, cs, sn);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) ss = fmaf(v[i], v[i], ss);
     ss = warp_sum(ss);
-    const float r = w != nullptr ? 1.0f / sqrtf(ss / (float)d + eps) : 1.0f;
+    float r = w != nullptr ? 1.0f / sqrtf(ss / (float)d + eps) : 1.0f;
+    const bool scaled = w != nullptr || (is_q && q_temp_every > 0);
+    if (is_q && q_temp_every > 0) r *= 1.0f + q_temp_coef * logf((float)((pos + 1) / q_temp_every + 1));
     T* dst = nullptr;
     long long vrow = -1;
     if (is_q) {
@@ -68,7 +95,7 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_kernel(
 #pragma unroll
         for (int i = 0; i < MAX_D / 32; ++i) {
             const int c = lane + 32 * i;
-            if (c < d) dst[c] = from_f<T>(w != nullptr ? v[i] * r * w[c] : v[i]);
+            if (c < d) dst[c] = from_f<T>(scaled ? v[i] * r * (w != nullptr ? w[c] : 1.0f) : v[i]);
         }
     }
     if (vrow >= 0) {
@@ -92,7 +119,9 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_vec_kernel(
     const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
     const T* __restrict__ v_other, long long v_other_stride, float lambda,
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots,
-    int n_units, int nh, int nkv, int d, int dv, int page_size, int lanes) {
+    int n_units, int nh, int nkv, int d, int dv, int page_size, int lanes,
+    const float* __restrict__ inv_freq, int rot_dims, float rot_mag, const int* __restrict__ positions,
+    float q_temp_coef, int q_temp_every) {
     pdl_wait_and_trigger();
     constexpr int VN = Vec16<T>::N;
     const int lane = threadIdx.x & 31;
@@ -108,12 +137,31 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_vec_kernel(
     const float* w = is_q ? q_w : k_w;
     float v[VN];
     load16<T>(x + li * VN, v);
+    const int pos = positions != nullptr ? positions[t] : 0;
+    if (rot_dims > 0) {
+        // a lane's VN entries are whole pairs
+#pragma unroll
+        for (int i = 0; i < VN; i += 2) {
+            const int c = li * VN + i;
+            if (c < rot_dims) {
+                float sn, cs;
+                sincosf((float)pos * inv_freq[c >> 1], &sn, &cs);
+                sn *= rot_mag;
+                cs *= rot_mag;
+                const float a = v[i], b = v[i + 1];
+                v[i] = rope_first(a, b, cs, sn);
+                v[i + 1] = rope_second(a, b, cs, sn);
+            }
+        }
+    }
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VN; ++i) ss = fmaf(v[i], v[i], ss);
     for (int o = lanes >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // within the unit's lanes
     if (!live) return;
-    const float r = w != nullptr ? 1.0f / sqrtf(ss / (float)d + eps) : 1.0f;
+    float r = w != nullptr ? 1.0f / sqrtf(ss / (float)d + eps) : 1.0f;
+    const bool scaled = w != nullptr || (is_q && q_temp_every > 0);
+    if (is_q && q_temp_every > 0) r *= 1.0f + q_temp_coef * logf((float)((pos + 1) / q_temp_every + 1));
     T* dst = nullptr;
     long long vrow = -1;
     if (is_q) {
@@ -129,7 +177,7 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_vec_kernel(
     if (dst != nullptr) {
         alignas(16) T o[VN];
 #pragma unroll
-        for (int i = 0; i < VN; ++i) o[i] = from_f<T>(w != nullptr ? v[i] * r * w[li * VN + i] : v[i]);
+        for (int i = 0; i < VN; ++i) o[i] = from_f<T>(scaled ? v[i] * r * (w != nullptr ? w[li * VN + i] : 1.0f) : v[i]);
         *reinterpret_cast<uint4*>(dst + li * VN) = *reinterpret_cast<const uint4*>(o);
     }
     if (vrow >= 0) {
@@ -159,7 +207,7 @@ __global__ __launch_bounds__(WARPS * 32) void attn_bias_kernel(
     const float* __restrict__ bias, int n_dist, const T* __restrict__ gate, long long gate_stride,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, const int* __restrict__ block_tables,
     const int* __restrict__ token_rows, int max_blocks, int n_rows, int nh, int nkv, int d, int dv, int page_size,
-    float scale, int window) {
+    float scale, int window, const float* __restrict__ sinks, const float* __restrict__ slopes) {
     pdl_wait();
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -176,6 +224,7 @@ __global__ __launch_bounds__(WARPS * 32) void attn_bias_kernel(
     __syncwarp();
 
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const float slope = slopes != nullptr ? slopes[h] : 0.f;
     float m = -INFINITY, l = 0.f;
     float acc[MAX_D / 32];
 #pragma unroll
@@ -197,6 +246,7 @@ __global__ __launch_bounds__(WARPS * 32) void attn_bias_kernel(
                 for (int j = 0; j < d; ++j) dot = fmaf(qs[j], to_f<T>(krow[j]), dot);
                 s = dot * scale;
                 if (bias != nullptr) s += bias[(size_t)min(pos - key, n_dist - 1) * nh + h];
+                if (slopes != nullptr) s -= slope * (float)(pos - key);
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -222,6 +272,15 @@ __global__ __launch_bounds__(WARPS * 32) void attn_bias_kernel(
         }
         m = m_new;
     }
+    if (sinks != nullptr) {
+        // one more term of the denominator, without a key or a value
+        const float sk = sinks[h];
+        const float m_new = fmaxf(m, sk);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= corr;
+    }
     float g = 1.0f;
     if (gate != nullptr) g = 1.0f / (1.0f + expf(-to_f<T>(gate[(size_t)t * gate_stride + h])));
     T* orow = out + ((size_t)t * nh + h) * dv;
@@ -243,9 +302,13 @@ extern "C" int rlis_qk_norm_store(const void* proj, long long stride, int q_off,
                                   const float* q_w, const float* k_w, float eps, const void* v_other,
                                   long long v_other_stride, float lambda, void* q_out, void* k_cache, void* v_cache,
                                   const int* slots, int n_tokens, int nh, int nkv, int d, int dv, int page_size,
-                                  int dtype, cudaStream_t stream) {
+                                  const float* inv_freq, int rot_dims, float rot_mag, const int* positions,
+                                  float q_temp_coef, int q_temp_every, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0 || d > MAX_D || dv <= 0 || nh <= 0 || nkv <= 0) return RLIS_ERR_UNSUPPORTED;
+    if (rot_dims < 0 || rot_dims > d || (rot_dims & 1) || (rot_dims > 0 && (inv_freq == nullptr || positions == nullptr)) ||
+        (q_temp_every > 0 && positions == nullptr))
+        return RLIS_ERR_UNSUPPORTED;
     const long long units = (long long)n_tokens * (nh + nkv);
     if (units > 0x7fffffffLL) return RLIS_ERR_UNSUPPORTED;
     {
@@ -264,11 +327,13 @@ extern "C" int rlis_qk_norm_store(const void* proj, long long stride, int q_off,
             if (dtype == RLIS_F32)
                 rlis_launch(qk_norm_store_vec_kernel<float>, vblocks, WARPS * 32, 0, stream, (const float*)proj, stride, q_off,
                             k_off, v_off, q_w, k_w, eps, (const float*)v_other, v_other_stride, lambda, (float*)q_out,
-                            (float*)k_cache, (float*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, lanes);
+                            (float*)k_cache, (float*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, lanes, inv_freq, rot_dims,
+                            rot_mag, positions, q_temp_coef, q_temp_every);
             else
                 rlis_launch(qk_norm_store_vec_kernel<bf16>, vblocks, WARPS * 32, 0, stream, (const bf16*)proj, stride, q_off,
                             k_off, v_off, q_w, k_w, eps, (const bf16*)v_other, v_other_stride, lambda, (bf16*)q_out,
-                            (bf16*)k_cache, (bf16*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, lanes);
+                            (bf16*)k_cache, (bf16*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, lanes, inv_freq, rot_dims,
+                            rot_mag, positions, q_temp_coef, q_temp_every);
             return RLIS_LAUNCH_CHECK();
         }
     }
@@ -276,23 +341,27 @@ extern "C" int rlis_qk_norm_store(const void* proj, long long stride, int q_off,
     if (dtype == RLIS_F32)
         rlis_launch(qk_norm_store_kernel<float>, blocks, WARPS * 32, 0, stream, (const float*)proj, stride, q_off, k_off,
                     v_off, q_w, k_w, eps, (const float*)v_other, v_other_stride, lambda, (float*)q_out, (float*)k_cache,
-                    (float*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size);
+                    (float*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, inv_freq, rot_dims, rot_mag, positions,
+                    q_temp_coef, q_temp_every);
     else if (dtype == RLIS_BF16)
         rlis_launch(qk_norm_store_kernel<bf16>, blocks, WARPS * 32, 0, stream, (const bf16*)proj, stride, q_off, k_off,
                     v_off, q_w, k_w, eps, (const bf16*)v_other, v_other_stride, lambda, (bf16*)q_out, (bf16*)k_cache,
-                    (bf16*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size);
+                    (bf16*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, inv_freq, rot_dims, rot_mag, positions,
+                    q_temp_coef, q_temp_every);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();
 }
 
 // q [T, nh d]; k_cache [pages, nkv, page_size, d]; v_cache [pages, nkv, page_size, dv]; out [T, nh dv];
-// bias float32 [n_dist, nh] or null; gate (null: none): logits, head h of token t at gate[t * gate_stride + h].
+// bias float32 [n_dist, nh] or null; gate (null: none): logits, head h of token t at gate[t * gate_stride + h];
+// sinks, slopes float32 [nh] or null.
 extern "C" int rlis_attention_bias(const void* q, const void* k_cache, const void* v_cache, void* out,
                                    const float* bias, int n_dist, const void* gate, long long gate_stride,
                                    const int* seq_of_token, const int* positions, const int* block_tables,
                                    const int* token_rows, int max_blocks, int n_tokens, int nh, int nkv, int d, int dv,
-                                   int page_size, float scale, int window, int dtype, cudaStream_t stream) {
+                                   int page_size, float scale, int window, const float* sinks, const float* slopes,
+                                   int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0 || d > MAX_D || dv <= 0 || dv > MAX_D || nkv <= 0 || nh % nkv != 0 || (bias != nullptr && n_dist <= 0))
         return RLIS_ERR_UNSUPPORTED;
@@ -303,11 +372,13 @@ extern "C" int rlis_attention_bias(const void* q, const void* k_cache, const voi
     if (dtype == RLIS_F32)
         rlis_launch(attn_bias_kernel<float>, blocks, WARPS * 32, smem, stream, (const float*)q, (const float*)k_cache,
                     (const float*)v_cache, (float*)out, bias, n_dist, (const float*)gate, gate_stride, seq_of_token,
-                    positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, dv, page_size, scale, window);
+                    positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, dv, page_size, scale, window,
+                    sinks, slopes);
     else if (dtype == RLIS_BF16)
         rlis_launch(attn_bias_kernel<bf16>, blocks, WARPS * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache,
                     (const bf16*)v_cache, (bf16*)out, bias, n_dist, (const bf16*)gate, gate_stride, seq_of_token,
-                    positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, dv, page_size, scale, window);
+                    positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, dv, page_size, scale, window,
+                    sinks, slopes);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

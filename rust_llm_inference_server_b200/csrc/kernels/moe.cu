@@ -3,6 +3,8 @@
 //   route:   z = W_r h (float32), s = sigmoid(z); the `top` experts with the largest s + correction are
 //            chosen (ties: the lower index); their weights are s * route_scale (no renormalisation).  An
 //            extra row of W_r, where given, is the logit of a gate on a shared expert: sigmoid of it.
+//            With `softmax_chosen`: z = W_r h + b_r; the `top` experts with the largest z (+ correction) are
+//            chosen and their weights are the softmax over the chosen logits alone, times route_scale.
 //   align:   the (token, choice) pairs are sorted by expert into slots; every expert's run of slots is
 //            padded to a multiple of the row tile (32 rows, or 128 when there are many pairs an expert),
 //            so a tile of rows belongs to one expert.  All on the device: no count ever reaches the
@@ -40,7 +42,8 @@ template <typename T, int TOK>
 __global__ __launch_bounds__(1024) void moe_route_kernel(
     const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ correction,
     int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ shared_gate,
-    int n_tokens, int width, int n_experts, int top, float route_scale) {
+    int n_tokens, int width, int n_experts, int top, float route_scale,
+    const float* __restrict__ router_bias, int softmax_chosen) {
     pdl_wait_and_trigger();
     extern __shared__ float sm[];
     const int stride = 2 * n_experts + 1;   // per token: z [n_experts + 1], choice [n_experts]
@@ -88,7 +91,8 @@ __global__ __launch_bounds__(1024) void moe_route_kernel(
     for (int idx = threadIdx.x; idx < TOK * n_experts; idx += blockDim.x) {
         const int i = idx / n_experts, e = idx - i * n_experts;
         float* z = sm + i * stride;
-        const float s = sigmoidf_(z[e]);
+        const float logit = z[e] + (router_bias != nullptr ? router_bias[e] : 0.f);
+        const float s = softmax_chosen ? logit : sigmoidf_(logit);
         z[e] = s;
         z[n_experts + 1 + e] = s + (correction != nullptr ? correction[e] : 0.f);
     }
@@ -116,10 +120,22 @@ __global__ __launch_bounds__(1024) void moe_route_kernel(
             if (at >= n_experts) at = k;        // scores that compare with nothing (NaN): still a valid index
             if (lane == 0) {
                 top_idx[(size_t)t * top + k] = at;
-                top_w[(size_t)t * top + k] = z[at] * route_scale;
+                top_w[(size_t)t * top + k] = softmax_chosen ? z[at] : z[at] * route_scale;
                 choice[at] = -INFINITY;
             }
             __syncwarp();
+        }
+        if (softmax_chosen && lane == 0) {
+            // what is there so far are the chosen logits, the largest first
+            float* wt = top_w + (size_t)t * top;
+            const float zmax = wt[0];
+            float sum = 0.f;
+            for (int k = 0; k < top; ++k) {
+                const float e = expf(wt[k] - zmax);
+                wt[k] = e;
+                sum += e;
+            }
+            for (int k = 0; k < top; ++k) wt[k] = wt[k] / sum * route_scale;
         }
     }
 }
@@ -313,7 +329,8 @@ __global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, in
 // float32 [T] or null.
 extern "C" int rlis_moe_route(const void* x, const float* w_router, const float* correction, int* top_idx,
                               float* top_w, float* shared_gate, int n_tokens, int width, int n_experts, int top,
-                              float route_scale, int dtype, cudaStream_t stream) {
+                              float route_scale, const float* router_bias, int softmax_chosen, int dtype,
+                              cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 512) return RLIS_ERR_UNSUPPORTED;
     // eight tokens a CTA when there are many (the router matrix is then read an eighth as often), one otherwise
@@ -324,7 +341,8 @@ extern "C" int rlis_moe_route(const void* x, const float* w_router, const float*
     const int rows = n_experts + (shared_gate != nullptr ? 1 : 0);
     const unsigned threads = 32u * (unsigned)(rows < 32 ? (rows < tok ? tok : rows) : 32);
 #define RLIS_ROUTE(T, TOK) rlis_launch(moe_route_kernel<T, TOK>, blocks, threads, smem, stream, (const T*)x, w_router, correction, \
-                                       top_idx, top_w, shared_gate, n_tokens, width, n_experts, top, route_scale)
+                                       top_idx, top_w, shared_gate, n_tokens, width, n_experts, top, route_scale, \
+                                       router_bias, softmax_chosen)
     if (dtype == RLIS_F32) { if (tok == 8) RLIS_ROUTE(float, 8); else RLIS_ROUTE(float, 1); }
     else if (dtype == RLIS_BF16) { if (tok == 8) RLIS_ROUTE(bf16, 8); else RLIS_ROUTE(bf16, 1); }
     else return RLIS_ERR_UNSUPPORTED;

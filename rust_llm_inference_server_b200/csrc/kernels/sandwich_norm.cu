@@ -9,6 +9,12 @@
 // no w_next, out is the stream itself rounded to the activation type (for sublayers that read the stream
 // as it is); without `sub` nothing is added and only that copy is made.
 //
+// sum_norm, one CTA a token, for blocks that norm the sum of the stream and a sublayer's result, and for
+// sublayers that are several branches side by side:
+//   y     = alpha * resid + ca * N(a; wa) + cb * N(b; wb)          N(x; w) = x / sqrt(mean(x^2) + eps) * w, or x itself
+//   y     = y / sqrt(mean(y^2) + eps_out) * w_out                  (only if w_out is given)      when w is null
+//   resid = y (float32, in place), out = y rounded to the activation type; every one of resid, a, b, out optional.
+//
 // act_norm, one CTA a token: out = x / sqrt(mean(x^2) + eps) * w (* sigmoid(gate)), x float32 or the
 // activation type with a row stride of its own, gate in the activation type with a row stride.
 #include "common.cuh"
@@ -104,6 +110,83 @@ __global__ __launch_bounds__(THREADS) void act_norm_kernel(
             if (grow != nullptr) y *= 1.0f / (1.0f + expf(-to_f<T>(grow[c])));
             orow[c] = from_f<T>(y);
         }
+    }
+}
+
+template <typename T>
+__global__ __launch_bounds__(THREADS) void sum_norm_kernel(
+    const T* __restrict__ a, const float* __restrict__ wa, float ca, const T* __restrict__ b,
+    const float* __restrict__ wb, float cb, float* __restrict__ resid, float alpha, const float* __restrict__ w_out,
+    T* __restrict__ out, int hidden, float eps_branch, float eps_out) {
+    pdl_wait_and_trigger();
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float va[MAX_PER_THREAD], vb[MAX_PER_THREAD];
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_THREAD; ++i) {
+        const int c = threadIdx.x + i * THREADS;
+        va[i] = vb[i] = 0.f;
+        if (c < hidden) {
+            if (a != nullptr) va[i] = to_f<T>(a[base + c]);
+            if (b != nullptr) vb[i] = to_f<T>(b[base + c]);
+            sa = fmaf(va[i], va[i], sa);
+            sb = fmaf(vb[i], vb[i], sb);
+        }
+    }
+    float ra = ca, rb = cb;
+    if (a != nullptr && wa != nullptr) ra = ca / sqrtf(block_sum(sa, scratch) / (float)hidden + eps_branch);
+    if (b != nullptr && wb != nullptr) rb = cb / sqrtf(block_sum(sb, scratch) / (float)hidden + eps_branch);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_THREAD; ++i) {
+        const int c = threadIdx.x + i * THREADS;
+        if (c < hidden) {
+            float y = resid != nullptr ? alpha * resid[base + c] : 0.f;
+            if (a != nullptr) y = fmaf(va[i] * ra, wa != nullptr ? wa[c] : 1.0f, y);
+            if (b != nullptr) y = fmaf(vb[i] * rb, wb != nullptr ? wb[c] : 1.0f, y);
+            va[i] = y;
+            ss = fmaf(y, y, ss);
+        }
+    }
+    float r = 1.0f;
+    if (w_out != nullptr) r = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps_out);
+#pragma unroll
+    for (int i = 0; i < MAX_PER_THREAD; ++i) {
+        const int c = threadIdx.x + i * THREADS;
+        if (c < hidden) {
+            const float y = w_out != nullptr ? va[i] * r * w_out[c] : va[i];
+            if (resid != nullptr) resid[base + c] = y;
+            if (out != nullptr) out[base + c] = from_f<T>(y);
+        }
+    }
+}
+
+// out[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * w * act(gate[t, h, :]): a norm per head with one
+// weight vector for all heads, and a gate (act 0: sigmoid, 1: silu = z sigmoid(z)).  One warp a (token, head).
+template <typename T>
+__global__ __launch_bounds__(128) void head_norm_gate_kernel(
+    const float* __restrict__ x, const float* __restrict__ w, const T* __restrict__ gate, long long gate_stride,
+    T* __restrict__ out, int n_units, int nh, int dv, float eps, int act) {
+    pdl_wait_and_trigger();
+    const int unit = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (unit >= n_units) return;
+    const int t = unit / nh, h = unit - t * nh;
+    const float* xr = x + (size_t)unit * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(xr[c], xr[c], ss);
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)dv + eps);
+    const T* g = gate != nullptr ? gate + (size_t)t * gate_stride + (size_t)h * dv : nullptr;
+    T* o = out + (size_t)unit * dv;
+    for (int c = lane; c < dv; c += 32) {
+        float y = xr[c] * r * w[c];
+        if (g != nullptr) {
+            const float z = to_f<T>(g[c]);
+            const float sg = 1.0f / (1.0f + expf(-z));
+            y *= act == 1 ? z * sg : sg;
+        }
+        o[c] = from_f<T>(y);
     }
 }
 
@@ -359,6 +442,44 @@ extern "C" int rlis_bias_act(const void* x, const float* b, void* out, long long
         rlis_launch(bias_act_kernel<float>, blocks, 256, 0, stream, (const float*)x, b, (float*)out, n, width, act);
     else if (dtype == RLIS_BF16)
         rlis_launch(bias_act_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)x, b, (bf16*)out, n, width, act);
+    else
+        return RLIS_ERR_UNSUPPORTED;
+    return RLIS_LAUNCH_CHECK();
+}
+
+// a, b: sublayer results [T, hidden] in the activation type (null: none); wa, wb: their norms' weights (null: the
+// result joins as it is); resid float32 [T, hidden] (null: no stream term, nothing written back); w_out null: no
+// norm of the sum; out null: no rounded copy.
+extern "C" int rlis_sum_norm(const void* a, const float* wa, float ca, const void* b, const float* wb, float cb,
+                             float* resid, float alpha, const float* w_out, void* out, int n_tokens, int hidden,
+                             float eps_branch, float eps_out, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hidden <= 0 || hidden > THREADS * MAX_PER_THREAD || (resid == nullptr && out == nullptr)) return RLIS_ERR_UNSUPPORTED;
+    if (dtype == RLIS_F32)
+        rlis_launch(sum_norm_kernel<float>, n_tokens, THREADS, 0, stream, (const float*)a, wa, ca, (const float*)b, wb, cb,
+                    resid, alpha, w_out, (float*)out, hidden, eps_branch, eps_out);
+    else if (dtype == RLIS_BF16)
+        rlis_launch(sum_norm_kernel<bf16>, n_tokens, THREADS, 0, stream, (const bf16*)a, wa, ca, (const bf16*)b, wb, cb,
+                    resid, alpha, w_out, (bf16*)out, hidden, eps_branch, eps_out);
+    else
+        return RLIS_ERR_UNSUPPORTED;
+    return RLIS_LAUNCH_CHECK();
+}
+
+// x float32 [T, nh, dv] contiguous; w float32 [dv]; gate (null: none) in the activation type, head h of token t
+// at gate + t * gate_stride + h * dv; out [T, nh, dv] in the activation type.
+extern "C" int rlis_head_norm_gate(const float* x, const float* w, const void* gate, long long gate_stride, void* out,
+                                   int n_tokens, int nh, int dv, float eps, int act, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const long long units = (long long)n_tokens * nh;
+    if (nh <= 0 || dv <= 0 || units > 0x7fffffffLL || act < 0 || act > 1) return RLIS_ERR_UNSUPPORTED;
+    const unsigned blocks = (unsigned)((units + 3) / 4);
+    if (dtype == RLIS_F32)
+        rlis_launch(head_norm_gate_kernel<float>, blocks, 128, 0, stream, x, w, (const float*)gate, gate_stride, (float*)out,
+                    (int)units, nh, dv, eps, act);
+    else if (dtype == RLIS_BF16)
+        rlis_launch(head_norm_gate_kernel<bf16>, blocks, 128, 0, stream, x, w, (const bf16*)gate, gate_stride, (bf16*)out,
+                    (int)units, nh, dv, eps, act);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

@@ -271,6 +271,104 @@ def act_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
     return out
 
 
+def sum_norm(resid: torch.Tensor | None, alpha: float, branches, w_out: torch.Tensor | None, eps_out: float,
+             out: torch.Tensor | None = None, eps_branch: float = 0.0) -> torch.Tensor | None:
+    """y = alpha * resid + sum over `branches` (x, w, c) of c * (x / sqrt(mean(x^2) + eps_branch) * w, or x itself
+    where w is None); with `w_out`, y = y / sqrt(mean(y^2) + eps_out) * w_out.  y is written back to `resid`
+    (float32 [T, H], in place; None: there is no stream term) and, rounded once, to `out` (the activation type;
+    None: no copy).  Up to two branches [T, H] in the activation type; all sums float32."""
+    branches = list(branches)
+    if len(branches) > 2:
+        raise KernelError("sum_norm: up to two branches")
+    ref = resid if resid is not None else out
+    if ref is None:
+        raise KernelError("sum_norm: nothing to write")
+    T, H = ref.shape
+    if resid is not None:
+        _req(resid, "resid", torch.float32, (T, H))
+    dtype = out.dtype if out is not None else (branches[0][0].dtype if branches else torch.float32)
+    if out is not None:
+        _req(out, "out", dtype, (T, H))
+    args = []
+    for x, w, c in branches:
+        _req(x, "branch", dtype, (T, H))
+        if w is not None:
+            _req(w, "branch weight", torch.float32, (H,))
+        args += [x.data_ptr(), w.data_ptr() if w is not None else None, float(c)]
+    while len(args) < 6:
+        args += [None, None, 0.0]
+    if w_out is not None:
+        _req(w_out, "w_out", torch.float32, (H,))
+    check(lib().rlis_sum_norm(*args, resid.data_ptr() if resid is not None else None, float(alpha),
+                              w_out.data_ptr() if w_out is not None else None,
+                              out.data_ptr() if out is not None else None, T, H, float(eps_branch), float(eps_out),
+                              _code(dtype), _stream()), "sum_norm")
+    _count("sum_norm" + (".%d" % len(branches)) + (".norm" if w_out is not None else ""))
+    return out if out is not None else resid
+
+
+GATE_ACTIVATIONS = {"sigmoid": 0, "silu": 1}
+
+
+def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, n_heads: int,
+                   gate: torch.Tensor | None = None, activation: str = "sigmoid") -> torch.Tensor:
+    """out[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * weight * act(gate[t, h, :]): one norm a head,
+    one weight vector [dv] for all heads.  x float32 [T, nh dv]; gate [T, nh dv] in out's type (may be a column
+    slice of wider rows); activation "sigmoid" or "silu"."""
+    T, W = x.shape
+    dv = W // n_heads
+    _req(x, "x", torch.float32, (T, n_heads * dv))
+    _req(weight, "weight", torch.float32, (dv,))
+    _req(out, "out", None, (T, W))
+    gp, gs = None, 0
+    if gate is not None:
+        if gate.dtype != out.dtype or tuple(gate.shape) != (T, W) or gate.stride(1) != 1 or not gate.is_cuda:
+            raise KernelError("head_norm_gate: the gate must be [T, nh dv] rows with unit stride in out's type")
+        gp, gs = gate.data_ptr(), gate.stride(0)
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"head_norm_gate: unknown activation {activation!r}; known: {sorted(GATE_ACTIVATIONS)}")
+    check(lib().rlis_head_norm_gate(x.data_ptr(), weight.data_ptr(), gp, gs, out.data_ptr(), T, n_heads, dv, float(eps),
+                                    GATE_ACTIVATIONS[activation], _code(out.dtype), _stream()), "head_norm_gate")
+    _count("head_norm_gate")
+    return out
+
+
+def gated_delta_state_floats(n_heads: int, n_qk_heads: int, d: int, dv: int, taps: int) -> int:
+    """float32 entries of a request's state for `gated_delta`: S of every head, then the convolution's tail."""
+    return n_heads * dv * d + (taps - 1) * (2 * n_qk_heads * d + n_heads * dv)
+
+
+def gated_delta(proj: torch.Tensor, qkv_off: int, b_off: int, a_off: int, conv_w: torch.Tensor, a_log: torch.Tensor,
+                dt_bias: torch.Tensor, state: torch.Tensor, out: torch.Tensor, step, n_heads: int, n_qk_heads: int,
+                d: int, dv: int, taps: int, unit_eps: float, q_scale: float) -> torch.Tensor:
+    """The gated delta rule over the step's tokens (csrc/kernels/gated_delta.cu): from the rows of a stacked
+    projection `proj` [T, N] (q | k | v from column qkv_off: n_qk_heads heads of d twice, then n_heads of dv; one
+    logit a head of beta from b_off and of the decay from a_off), a causal convolution of `taps` taps per channel
+    (conv_w float32 [C, taps]) and silu, unit vectors q (times q_scale) and k, then per head S <- g S, u = beta
+    (v - S^T k), S <- S + k u^T, o = S^T q.  `state` float32 [slots, gated_delta_state_floats(...)] holds S and
+    the convolution's tail between steps; out float32 [T, nh dv]."""
+    T, N = proj.shape
+    C = 2 * n_qk_heads * d + n_heads * dv
+    _req(proj, "proj")
+    _req(conv_w, "conv_w", torch.float32, (C, taps))
+    _req(a_log, "a_log", torch.float32, (n_heads,))
+    _req(dt_bias, "dt_bias", torch.float32, (n_heads,))
+    _req(out, "out", torch.float32, (T, n_heads * dv))
+    _req(state, "state", torch.float32, (None, gated_delta_state_floats(n_heads, n_qk_heads, d, dv, taps)))
+    if qkv_off + C > N or b_off + n_heads > N or a_off + n_heads > N:
+        raise KernelError("gated_delta: the column offsets reach beyond the projection's rows")
+    act = step.buffer("gated_delta_act", (T, C + 2 * n_heads), torch.float32)
+    check(lib().rlis_gated_delta(proj.data_ptr(), proj.stride(0), int(qkv_off), int(b_off), int(a_off), conv_w.data_ptr(),
+                                 a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), state.stride(0),
+                                 step.cu_seqlens.data_ptr(), step.ctx_lens.data_ptr(), step.state_slots.data_ptr(),
+                                 step.seq_of_token.data_ptr(), act.data_ptr(), out.data_ptr(), T, step.n_seqs, n_heads,
+                                 n_qk_heads, d, dv, taps, float(unit_eps), float(q_scale), _code(proj.dtype), _stream()),
+          "gated_delta")
+    _count("gated_delta.prepare")
+    _count("gated_delta.scan")
+    return out
+
+
 BIAS_ACTIVATIONS = {"none": 0, "relu2": 1}
 
 
@@ -975,12 +1073,19 @@ def glu_act(gate_up: torch.Tensor, out: torch.Tensor, slope: float = 1.0, limit:
 
 def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w, k_w, eps: float, v_other, lam: float,
                   q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slots, n_heads: int,
-                  n_kv_heads: int, dim: int, v_dim: int, page_size: int) -> torch.Tensor:
+                  n_kv_heads: int, dim: int, v_dim: int, page_size: int, rotation: tuple | None = None,
+                  positions: torch.Tensor | None = None, q_temp: tuple | None = None) -> torch.Tensor:
     """From the rows of a stacked projection `proj` [T, N] (queries at column q_off, keys at k_off, values
     at v_off): q_out [T, nh dim] = per-head rmsnorm(q) * q_w, and at `slots` of the paged caches the keys
     rmsnorm(k) * k_w and the values, mixed as (1 - lam) v + lam v_other where `v_other` (a [T, nkv v_dim]
     column slice of another projection's rows) is given.  q_w, k_w float32 [dim] or None (no norm); slots
-    None: nothing is stored.  Statistics and the mixing are float32."""
+    None: nothing is stored.  Statistics and the mixing are float32.
+
+    `rotation` = (float32 frequencies [r / 2], r, multiplier): before the norm, entries (2i, 2i + 1) of every
+    query and key head, i < r / 2, turn by the angle position * frequency i, cos and sin times the multiplier
+    (values are taken as projected, so v_off = k_off caches the unrotated keys as values).  `q_temp` = (coef,
+    every): queries are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1) at position p.  Both take
+    `positions` (int32 [T])."""
     T, N = proj.shape
     _req(proj, "proj")
     _req(q_out, "q_out", proj.dtype, (T, n_heads * dim))
@@ -999,14 +1104,24 @@ def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w, k
                 or not v_other.is_cuda):
             raise KernelError("qk_norm_store: the other layer's values must be [T, nkv v_dim] rows with unit stride")
         vo, vo_stride = v_other.data_ptr(), v_other.stride(0)
+    inv_freq, rot_dims, rot_mag = rotation if rotation is not None else (None, 0, 1.0)
+    if rot_dims:
+        _req(inv_freq, "rotation frequencies", torch.float32, (rot_dims // 2,))
+        if rot_dims % 2 or rot_dims > dim:
+            raise KernelError(f"qk_norm_store: {rot_dims} rotated entries do not fit heads of {dim} in pairs")
+    coef, every = q_temp if q_temp is not None else (0.0, 0)
+    if rot_dims or every:
+        _req(positions, "positions", torch.int32, (T,))
     check(lib().rlis_qk_norm_store(proj.data_ptr(), N, int(q_off), int(k_off), int(v_off),
                                    q_w.data_ptr() if q_w is not None else None,
                                    k_w.data_ptr() if k_w is not None else None, float(eps), vo, vo_stride, float(lam),
                                    q_out.data_ptr(), k_cache.data_ptr() if slots is not None else None,
                                    v_cache.data_ptr() if slots is not None else None,
                                    slots.data_ptr() if slots is not None else None, T, n_heads, n_kv_heads, dim, v_dim,
-                                   page_size, _code(proj.dtype), _stream()), "qk_norm_store")
-    _count("qk_norm_store" + (".mix" if v_other is not None else ""))
+                                   page_size, inv_freq.data_ptr() if rot_dims else None, int(rot_dims), float(rot_mag),
+                                   positions.data_ptr() if (rot_dims or every) else None, float(coef), int(every),
+                                   _code(proj.dtype), _stream()), "qk_norm_store")
+    _count("qk_norm_store" + (".mix" if v_other is not None else "") + (".rot" if rot_dims else ""))
     return q_out
 
 
@@ -1018,10 +1133,11 @@ def _biased_mma_sizes(dim: int, v_dim: int) -> bool:
     return bool(lib().rlis_attention_bias_mma_takes(dim, v_dim))
 
 
-def biased_attention_takes_mma(dtype, n_heads: int, n_kv_heads: int, dim: int, v_dim: int) -> bool:
-    """Whether the tensor-core kernels for attention with a bias by distance exist for these sizes."""
+def biased_attention_takes_mma(dtype, n_heads: int, n_kv_heads: int, dim: int, v_dim: int, sinks: bool = False,
+                               slopes: bool = False) -> bool:
+    """Whether the tensor-core kernels for attention with a bias by distance exist for these sizes and options."""
     return bool(BIASED_MMA and dtype == torch.bfloat16 and n_heads % n_kv_heads == 0
-                and _biased_mma_sizes(int(dim), int(v_dim)))
+                and _biased_mma_sizes(int(dim), int(v_dim)) and not sinks and not slopes)
 
 
 @functools.lru_cache(maxsize=4096)
@@ -1037,10 +1153,12 @@ def biased_decode_pieces(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
 
 
 def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_heads: int, n_kv_heads: int,
-                     dim: int, v_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
+                     dim: int, v_dim: int, page_size: int, scale: float, window: int = 0,
+                     sinks: torch.Tensor | None = None, slopes: torch.Tensor | None = None) -> torch.Tensor:
     """Causal grouped-query attention of every token of the step over its request's cached keys:
-    score = scale * q . k + bias[min(distance, len(bias) - 1), head]; a head's result is multiplied by
-    sigmoid(gate[t, head]).  q [T, nh dim]; k_cache [pages, nkv, page_size, dim]; v_cache [pages, nkv,
+    score = scale * q . k + bias[min(distance, len(bias) - 1), head] - slopes[head] * distance; a head's
+    result is multiplied by sigmoid(gate[t, head]); exp(sinks[head]) joins the softmax's denominator
+    (`slopes`, `sinks` float32 [nh] or None).  q [T, nh dim]; k_cache [pages, nkv, page_size, dim]; v_cache [pages, nkv,
     page_size, v_dim]; out [T, nh v_dim]; bias float32 [n_dist, nh] or None; gate [T, nh] (a column slice
     of wider rows) or None.
 
@@ -1061,8 +1179,13 @@ def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_h
         if gate.dtype != q.dtype or tuple(gate.shape) != (T, n_heads) or gate.stride(1) != 1 or not gate.is_cuda:
             raise KernelError("attention_biased: the gate must be [T, nh] rows with unit stride in q's type")
         gp, gs = gate.data_ptr(), gate.stride(0)
+    for v, nm in ((sinks, "sinks"), (slopes, "slopes")):
+        if v is not None:
+            _req(v, nm, torch.float32, (n_heads,))
+    sp = sinks.data_ptr() if sinks is not None else None
+    lp = slopes.data_ptr() if slopes is not None else None
     tables = step.block_tables[group]
-    fast = biased_attention_takes_mma(q.dtype, n_heads, n_kv_heads, dim, v_dim)
+    fast = biased_attention_takes_mma(q.dtype, n_heads, n_kv_heads, dim, v_dim, sinks is not None, slopes is not None)
     n_dec = getattr(step, "n_decode", 0) if fast and n_heads // n_kv_heads <= 16 else 0
     n_tiles = getattr(step, "n_prefill_tiles", 0) if fast else 0
     if n_dec:
@@ -1096,8 +1219,8 @@ def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_h
     check(lib().rlis_attention_bias(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), bp, n_dist, gp,
                                     gs, step.seq_of_token.data_ptr(), step.positions.data_ptr(), tables.data_ptr(),
                                     rows.data_ptr() if rows is not None else None, tables.shape[1], n_rows, n_heads,
-                                    n_kv_heads, dim, v_dim, page_size, float(scale), int(window), _code(q.dtype),
-                                    _stream()), "attention_bias")
+                                    n_kv_heads, dim, v_dim, page_size, float(scale), int(window), sp, lp,
+                                    _code(q.dtype), _stream()), "attention_bias")
     _count("attention_bias")
     return out
 
@@ -1138,9 +1261,11 @@ def _moe_gemm(a, wg_ptr: int, wu_ptr, w_stride: int, interleave: int, out, plan,
 
 
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: int, top: int, route_scale: float,
-              shared_gate: bool, step) -> MoePlan:
-    """Scores s = sigmoid(w_router x) in float32; the `top` experts with the largest s + correction; weights
-    s * route_scale.  w_router float32 [n_experts (+ 1), width]: with `shared_gate` its last row is the logit
+              shared_gate: bool, step, router_bias: torch.Tensor | None = None,
+              softmax_chosen: bool = False) -> MoePlan:
+    """Scores s = sigmoid(w_router x + router_bias) in float32; the `top` experts with the largest s +
+    correction; weights s * route_scale.  `softmax_chosen`: the logits themselves are the scores, and the
+    weights are the softmax over the chosen logits alone (times route_scale).  w_router float32 [n_experts (+ 1), width]: with `shared_gate` its last row is the logit
     of the shared expert's gate.  Then the pairs are sorted by expert on the device."""
     T, W = x.shape
     _req(x, "x")
@@ -1148,6 +1273,8 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: in
     _req(w_router, "w_router", torch.float32, (rows, W))
     if correction is not None:
         _req(correction, "correction", torch.float32, (n_experts,))
+    if router_bias is not None:
+        _req(router_bias, "router_bias", torch.float32, (n_experts,))
     pairs = T * top
     tile = moe_tile_rows(pairs, n_experts)
     max_tiles = min(pairs, n_experts) + pairs // tile      # every expert in use ends in at most one partial tile
@@ -1159,7 +1286,9 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: in
     top_w, gate = flts[:pairs], flts[pairs:]
     check(lib().rlis_moe_route(x.data_ptr(), w_router.data_ptr(), correction.data_ptr() if correction is not None else None,
                                top_idx.data_ptr(), top_w.data_ptr(), gate.data_ptr() if shared_gate else None, T, W,
-                               n_experts, top, float(route_scale), _code(x.dtype), _stream()), "moe_route")
+                               n_experts, top, float(route_scale),
+                               router_bias.data_ptr() if router_bias is not None else None, 1 if softmax_chosen else 0,
+                               _code(x.dtype), _stream()), "moe_route")
     _count("moe_route")
     check(lib().rlis_moe_align(top_idx.data_ptr(), sorted_pair.data_ptr(), pair_slot.data_ptr(), tile_expert.data_ptr(),
                                pairs, n_experts, max_tiles, tile, _stream()), "moe_align")

@@ -30,6 +30,10 @@ SIGNATURES = {
     "rlis_gemm_f32_nt": [P, P, P, I, I, I, P],
     "rlis_gemm_f32_nt_batched": [P, P, P, I, I, I, LL, LL, LL, I, LL, LL, LL, P],
     "rlis_post_norm_residual": [P, P, P, P, P, P, P, I, I, F, F, F, I, P],
+    "rlis_sum_norm": [P, P, F, P, P, F, P, F, P, P, I, I, F, F, I, P],
+    "rlis_head_norm_gate": [P, P, P, LL, P, I, I, I, F, I, I, P],
+    "rlis_gated_delta": [P, LL, I, I, I, P, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, I, P],
+    "rlis_gated_delta_state_floats": [I, I, I, I, I],
     "rlis_act_norm": [P, LL, I, P, P, LL, P, LL, I, I, F, I, P],
     "rlis_bias_act": [P, P, P, LL, I, I, I, P],
     "rlis_latent_kv_store": [P, LL, P, P, P, P, P, I, I, I, I, F, F, I, P, P, P, I, P],
@@ -39,12 +43,12 @@ SIGNATURES = {
     "rlis_attention_latent_prefill": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
     "rlis_attention_latent_decode": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_lightning_scan": [P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P, I, P],
-    "rlis_qk_norm_store": [P, LL, I, I, I, P, P, F, P, LL, F, P, P, P, P, I, I, I, I, I, I, I, P],
-    "rlis_attention_bias": [P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
+    "rlis_qk_norm_store": [P, LL, I, I, I, P, P, F, P, LL, F, P, P, P, P, I, I, I, I, I, I, P, I, F, P, F, I, I, P],
+    "rlis_attention_bias": [P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, P],
     "rlis_attention_bias_mma_takes": [I, I],
     "rlis_attention_bias_prefill": [P, P, P, P, P, I, P, LL, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
     "rlis_attention_bias_decode": [P, P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
-    "rlis_moe_route": [P, P, P, P, P, P, I, I, I, I, F, I, P],
+    "rlis_moe_route": [P, P, P, P, P, P, I, I, I, I, F, P, I, I, P],
     "rlis_moe_align": [P, P, P, P, I, I, I, I, P],
     "rlis_moe_gemm": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, LL, I, I, P],
     "rlis_moe_gather_rows": [P, P, P, I, I, I, I, P],

@@ -1,6 +1,7 @@
-"""Causal grouped-query attention without rotation: per-head RMS norms of queries and keys, a learned
-bias by distance, values of their own width that a layer may mix with another layer's, and a gate on
-every head's output."""
+"""Causal grouped-query attention with per-head RMS norms of queries and keys, a learned bias by
+distance, values of their own width that a layer may mix with another layer's, and a gate on every head's
+output; optionally a rotation of part of every head before the norms, keys that double as values, a query
+temperature by position, a penalty linear in the distance, a window, and a sink in the softmax."""
 
 from __future__ import annotations
 
@@ -11,7 +12,7 @@ import torch
 
 from .. import ops
 from ..ops.profile import span
-from .base import KVCacheSpec, Mixer, register_mixer
+from .base import KVCacheSpec, Mixer, build_position, register_mixer
 
 
 def log_bucket(n: int, rows: int, far: float) -> int:
@@ -65,13 +66,45 @@ class BiasedAttention(Mixer):
         self.k_off = spec.n_heads * spec.dim
         self.v_off = self.k_off + spec.n_kv_heads * spec.dim
         self.g_off = self.v_off + spec.n_kv_heads * spec.v_dim
+        if spec.v_proj is None:
+            # the values are the keys as projected: the same columns, read before rotation and norm
+            if spec.v_dim != spec.dim or spec.value_mix is not None or spec.value_source:
+                raise ValueError("keys that double as values have the keys' width and are not mixed with another layer's")
+            self.v_off = self.k_off
+            self.g_off = self.k_off + spec.n_kv_heads * spec.dim
         self.lam = 0.0
-        self.bias = self.q_w = self.k_w = None
+        self.bias = self.q_w = self.k_w = self.sinks = self.slopes = None
+        self.rotation = None
+        if spec.rotation is not None:
+            pos = build_position(spec.rotation, dtype, device)
+            if getattr(pos, "pairing", None) != "adjacent" or not hasattr(pos, "rotation"):
+                raise ValueError("this mixer rotates entry 2i with entry 2i + 1 (a rotary spec with pairing 'adjacent')")
+            self.rotation = pos.rotation()
+            if self.rotation[1] > spec.dim:
+                raise ValueError(f"the rotation covers {self.rotation[1]} entries, a head has {spec.dim}")
+        if spec.unit_norm and (spec.q_norm is not None or spec.k_norm is not None):
+            raise ValueError("queries and keys are normed with a weight or without, not both")
+        self.q_temp = None
+        if spec.q_temp is not None:
+            coef, every = float(spec.q_temp[0]), int(spec.q_temp[1])
+            if every <= 0:
+                raise ValueError(f"the query temperature steps every {every} positions")
+            self.q_temp = (coef, every)
+        if spec.slopes is not None:
+            if len(spec.slopes) != spec.n_heads:
+                raise ValueError(f"{len(spec.slopes)} slopes for {spec.n_heads} heads")
+            self.slopes = torch.tensor([float(v) for v in spec.slopes], dtype=torch.float64).to(torch.float32).to(device)
+        if spec.unit_norm:
+            self.q_w = self.k_w = torch.ones((spec.dim,), dtype=torch.float32, device=device)
 
     def tensors(self) -> dict:
         s = self.spec
         out = {s.q_proj: (s.n_heads * s.dim, s.hidden), s.k_proj: (s.n_kv_heads * s.dim, s.hidden),
-               s.v_proj: (s.n_kv_heads * s.v_dim, s.hidden), s.o_proj: (s.hidden, s.n_heads * s.v_dim)}
+               s.o_proj: (s.hidden, s.n_heads * s.v_dim)}
+        if s.v_proj is not None:
+            out[s.v_proj] = (s.n_kv_heads * s.v_dim, s.hidden)
+        if s.sink is not None:
+            out[s.sink] = (s.n_heads,)
         if s.q_norm is not None:
             out[s.q_norm] = (s.dim,)
         if s.k_norm is not None:
@@ -86,7 +119,7 @@ class BiasedAttention(Mixer):
 
     def load(self, src) -> None:
         s = self.spec
-        parts = [src.get(s.q_proj), src.get(s.k_proj), src.get(s.v_proj)]
+        parts = [src.get(s.q_proj), src.get(s.k_proj)] + ([src.get(s.v_proj)] if s.v_proj is not None else [])
         if s.head_gate is not None:
             parts.append(src.get(s.head_gate))
         w = torch.cat(parts, dim=0)
@@ -95,8 +128,11 @@ class BiasedAttention(Mixer):
             w = torch.cat([w, w.new_zeros((pad, w.shape[1]))], dim=0)
         self.w_in = w.contiguous()
         self.w_o = src.get(s.o_proj).contiguous()
-        self.q_w = src.get(s.q_norm, "vector").contiguous() if s.q_norm is not None else None
-        self.k_w = src.get(s.k_norm, "vector").contiguous() if s.k_norm is not None else None
+        if not s.unit_norm:
+            self.q_w = src.get(s.q_norm, "vector").contiguous() if s.q_norm is not None else None
+            self.k_w = src.get(s.k_norm, "vector").contiguous() if s.k_norm is not None else None
+        if s.sink is not None:
+            self.sinks = src.get(s.sink, "vector").contiguous()
         if s.bias is not None:
             self.bias = bias_by_distance(src.get(s.bias.table, "vector"), float(s.bias.far))
         if s.value_mix is not None:
@@ -108,7 +144,8 @@ class BiasedAttention(Mixer):
 
     def _fast(self) -> bool:
         s = self.spec
-        return ops.biased_attention_takes_mma(self.dtype, s.n_heads, s.n_kv_heads, s.dim, s.v_dim)
+        return ops.biased_attention_takes_mma(self.dtype, s.n_heads, s.n_kv_heads, s.dim, s.v_dim,
+                                              sinks=s.sink is not None, slopes=s.slopes is not None)
 
     @property
     def prefill_tile(self):
@@ -136,12 +173,14 @@ class BiasedAttention(Mixer):
         with span("q, k norms + value mix + kv write"):
             ops.qk_norm_store(proj, self.q_off, self.k_off, self.v_off, self.q_w, self.k_w, self.eps, other, self.lam, q,
                               cache.k, cache.v, step.slots[cache.group] if writes_cache else None, s.n_heads,
-                              s.n_kv_heads, s.dim, s.v_dim, cache.page_size)
+                              s.n_kv_heads, s.dim, s.v_dim, cache.page_size, rotation=self.rotation,
+                              positions=step.positions, q_temp=self.q_temp)
         o = step.buffer("attn_o", (T, s.n_heads * s.v_dim), self.dtype)
         gate = proj[:, self.g_off:self.g_off + s.n_heads] if s.head_gate is not None else None
         with span("attention"):
             ops.attention_biased(q, cache.k, cache.v, o, self.bias, gate, step, cache.group, s.n_heads, s.n_kv_heads,
-                                 s.dim, s.v_dim, cache.page_size, self.scale, self.window)
+                                 s.dim, s.v_dim, cache.page_size, self.scale, self.window, sinks=self.sinks,
+                                 slopes=self.slopes)
         with span("o proj"):
             return ops.linear(o, self.w_o)
 

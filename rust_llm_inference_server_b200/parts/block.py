@@ -163,6 +163,65 @@ class OutNormBlock:
         return resid, (StreamRows(h) if chained else None)
 
 
+class PostNormBlock:
+    """x = norm1(a x + mixer(x)); x = norm2(a x + feed_forward(x)), the second line only when the layer has a
+    feed-forward; a is a constant.  The sublayers read the stream as it is.  The stream, the sums and the norms
+    are float32: one kernel adds a sublayer's result to the scaled stream, norms the sum into the stream and
+    leaves the stream, rounded to the compute type, for the sublayer that follows (in float32 that sublayer reads
+    the stream itself).  A mixer of several branches (`forward_branches`) has its branches normed and averaged in
+    the same kernel.  A block returns no pending delta, and hands the next block of its kind the rounded stream."""
+
+    def __init__(self, spec, dtype, device):
+        self.dtype = dtype
+        self.alpha = float(spec.stream_mult)
+        self.hidden = spec.norm1.dim
+        self.mixer = build_mixer(spec.mixer, dtype, device)
+        self.norm1 = build_norm(spec.norm1, dtype, device)
+        self.feed_forward = build_feed_forward(spec.feed_forward, dtype, device) if spec.feed_forward is not None else None
+        self.norm2 = build_norm(spec.norm2, dtype, device) if self.feed_forward is not None else None
+        for n in (self.norm1, self.norm2):
+            if n is not None and not hasattr(n, "weight"):
+                raise ValueError("the postnorm arrangement takes norms that are a weight and an eps (RMSNorm)")
+
+    chains_norms = True      # `forward` takes `next_block`
+
+    def entry_sink(self, resid, step):
+        return None
+
+    def parts(self):
+        return tuple(p for p in (self.mixer, self.norm1, self.feed_forward, self.norm2) if p is not None)
+
+    def _stream(self, resid, step):
+        if self.dtype == torch.float32:
+            return resid
+        h = step.buffer("stream_copy", (resid.shape[0], self.hidden), self.dtype)
+        return ops.post_norm_residual(None, resid, None, 0.0, out=h)
+
+    def _join(self, terms, eps_branch, norm, resid, step, wanted: bool):
+        """resid = norm(alpha * resid + sum of the terms); returns the stream for the next sublayer if `wanted`."""
+        h = None
+        if wanted and self.dtype != torch.float32:
+            h = step.buffer("stream_copy", (resid.shape[0], self.hidden), self.dtype)
+        ops.sum_norm(resid, self.alpha, terms, norm.weight, norm.eps, out=h, eps_branch=eps_branch)
+        return (h if h is not None else resid) if wanted else None
+
+    def forward(self, resid, pending, step, cache, state, writes_cache=True, next_block=None):
+        h = pending.x if isinstance(pending, StreamRows) else self._stream(resid, step)
+        chained = isinstance(next_block, (PostNormBlock, OutNormBlock)) and next_block.dtype == self.dtype
+        branches = getattr(self.mixer, "forward_branches", None)
+        if branches is not None:
+            terms, eps_b = branches(h, step, cache, state, writes_cache)
+        else:
+            terms, eps_b = [(self.mixer.forward(h, step, cache, state, writes_cache), None, 1.0)], 0.0
+        if len(terms) > 2:
+            terms, eps_b = [(self.mixer.forward(h, step, cache, state, writes_cache), None, 1.0)], 0.0
+        h = self._join(terms, eps_b, self.norm1, resid, step, chained or self.feed_forward is not None)
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(h, step)
+            h = self._join([(f, None, 1.0)], 0.0, self.norm2, resid, step, chained)
+        return resid, (StreamRows(h) if chained else None)
+
+
 class StreamRows:
     """What an outnorm block hands the next one: `x`, the (complete) residual stream in the compute type."""
 
@@ -200,3 +259,4 @@ class _BlockTensors(Part):
 register_arrangement("prenorm", PreNormBlock)
 register_arrangement("sandwich", SandwichBlock)
 register_arrangement("outnorm", OutNormBlock)
+register_arrangement("postnorm", PostNormBlock)

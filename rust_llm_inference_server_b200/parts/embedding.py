@@ -7,11 +7,12 @@ import torch
 
 from .. import ops
 from ..ops.profile import span
-from .base import LogitsHead, TokenEmbedding, register_embedding, register_lm_head
+from .base import LogitsHead, TokenEmbedding, build_norm, register_embedding, register_lm_head
 
 
 class Embedding(TokenEmbedding):
-    """out[t, :] = weight[id_t, :] widened to float32, times `scale` where the spec gives one."""
+    """out[t, :] = weight[id_t, :] widened to float32, times `scale` where the spec gives one, then normed in
+    float32 where the spec names a norm."""
 
     graph_safe = True
 
@@ -19,23 +20,35 @@ class Embedding(TokenEmbedding):
         self.spec = spec
         self.scale = None if spec.scale is None else float(spec.scale)
         self.weight = None
+        self.norm = build_norm(spec.norm, dtype, device) if getattr(spec, "norm", None) is not None else None
+        if self.norm is not None and not hasattr(self.norm, "weight"):
+            raise ValueError("the embedding's norm is a weight and an eps (RMSNorm)")
 
     def tensors(self) -> dict:
-        return {self.spec.weight: (self.spec.vocab_size, self.spec.dim)}
+        out = {self.spec.weight: (self.spec.vocab_size, self.spec.dim)}
+        if self.norm is not None:
+            out.update(self.norm.tensors())
+        return out
 
     def load(self, src) -> None:
         self.weight = src.get(self.spec.weight, share=True).contiguous()
+        if self.norm is not None:
+            self.norm.load(src)
 
     def fuses_norms(self, step) -> bool:
         """True when `forward` takes a keyword `sink` in this step (the first block's first norm,
         an `ops.ResidualSink` over `out`) and returns that norm's `ops.ScaledRows`."""
-        return self.weight.dtype == torch.bfloat16 and ops.fuses_norms(step.n_tokens, self.weight.dtype, self.spec.dim)
+        return (self.norm is None and self.weight.dtype == torch.bfloat16
+                and ops.fuses_norms(step.n_tokens, self.weight.dtype, self.spec.dim))
 
     def forward(self, token_ids, out, step, sink=None):
         with span("embedding"):
             if sink is not None:
                 return ops.embedding_sink(token_ids, self.weight, out, self.scale, sink)
-            return ops.embedding(token_ids, self.weight, out, self.scale)
+            ops.embedding(token_ids, self.weight, out, self.scale)
+            if self.norm is not None:
+                ops.sum_norm(out, 1.0, [], self.norm.weight, self.norm.eps)
+            return out
 
 
 class LMHead(LogitsHead):

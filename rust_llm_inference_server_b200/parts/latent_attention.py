@@ -29,6 +29,8 @@ class LatentAttention(Mixer):
         self.dtype = dtype
         self.position = build_position(spec.position, dtype, device)
         rot = getattr(self.position, "rotation", None)
+        if getattr(self.position, "pairing", "half") != "half":
+            raise ValueError("latent attention rotates entry i with entry i + dims / 2")
         self.inv_freq, self.rot_dims, self.magnitude = rot() if rot is not None else (None, 0, 1.0)
         if self.inv_freq is None:
             self.inv_freq = torch.zeros((0,), dtype=torch.float32, device=device)

@@ -97,11 +97,15 @@ class NoPosition(PositionEncoding):
 
 class YarnRope(PositionEncoding):
     """A rotation a mixer applies itself: `rotation()` gives (float32 frequencies on the device, how
-    many leading entries are rotated, the multiplier of cos and sin)."""
+    many leading entries are rotated, the multiplier of cos and sin); `pairing` says which entries turn
+    together ("half" or "adjacent")."""
 
     def __init__(self, spec, dtype, device):
         if spec.dims <= 0 or spec.dims % 2:
-            raise ValueError(f"a rotate-half rotation takes an even number of entries, got {spec.dims}")
+            raise ValueError(f"a rotation in pairs takes an even number of entries, got {spec.dims}")
+        self.pairing = getattr(spec, "pairing", "half")
+        if self.pairing not in ("half", "adjacent"):
+            raise ValueError(f"a rotation pairs entries by 'half' or 'adjacent', got {self.pairing!r}")
         inv, self.magnitude = yarn_inverse_frequencies(spec.dims, spec.base, spec.factor, spec.original,
                                                        spec.fast, spec.slow)
         self.dims = int(spec.dims)

@@ -27,6 +27,9 @@ class RoutedFF(FeedForward):
         self.shared = build_feed_forward(spec.shared, dtype, device) if spec.shared is not None else None
         if spec.shared_gate is not None and self.shared is None:
             raise ValueError("a gate on the shared expert, and no shared expert")
+        if spec.scoring not in ("sigmoid", "softmax_chosen"):
+            raise ValueError(f"experts are scored by 'sigmoid' or 'softmax_chosen', got {spec.scoring!r}")
+        self.router_bias = None
 
     def _names(self, pattern: str):
         return [pattern.format(e=e) for e in range(self.spec.n_experts)]
@@ -36,6 +39,8 @@ class RoutedFF(FeedForward):
         out = {s.router: (s.n_experts, s.hidden)}
         if s.correction is not None:
             out[s.correction] = (s.n_experts,)
+        if s.router_bias is not None:
+            out[s.router_bias] = (s.n_experts,)
         for n in self._names(s.gate_proj) + self._names(s.up_proj):
             out[n] = (s.intermediate, s.hidden)
         for n in self._names(s.down_proj):
@@ -53,6 +58,7 @@ class RoutedFF(FeedForward):
             rows.append(src.get(s.shared_gate, "vector"))
         self.w_router = torch.cat(rows, dim=0).contiguous()              # float32 [experts (+ 1), hidden]
         self.correction = src.get(s.correction, "vector").contiguous() if s.correction is not None else None
+        self.router_bias = src.get(s.router_bias, "vector").contiguous() if s.router_bias is not None else None
         # one stack [expert, 2 I, in] of both branches: gate and linear rows interleaved in blocks of 4 (what
         # the gated epilogue of the grouped product over prompts wants) where I allows, else gate rows first
         I, W = s.intermediate, s.hidden
@@ -74,7 +80,8 @@ class RoutedFF(FeedForward):
         T = x.shape[0]
         with span("router"):
             plan = ops.moe_route(x, self.w_router, self.correction, s.n_experts, s.top, s.route_scale,
-                                 s.shared_gate is not None, step)
+                                 s.shared_gate is not None, step, router_bias=self.router_bias,
+                                 softmax_chosen=s.scoring == "softmax_chosen")
         y_shared = self.shared.forward(x, step) if self.shared is not None else None
         with span("experts"):
             act = ops.moe_up(x, self.w_gate_up, plan, s.slope, self.limit, s.up_shift, step, self.interleave)

@@ -40,13 +40,15 @@ class YarnRopeSpec:
     lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims - 1) and ramp_i = clamp((i - lo) /
     max(hi - lo, 0.001), 0, 1), frequency i is f_i / factor * ramp_i + f_i (1 - ramp_i), f_i =
     base^(-2i / dims), and cos and sin are multiplied by 0.1 ln(factor) + 1.  `factor` None: the plain
-    frequencies f_i and no multiplier."""
+    frequencies f_i and no multiplier.  `pairing` says which entries turn together: "half" (entry i with
+    entry i + dims / 2) or "adjacent" (entry 2i with entry 2i + 1); a mixer takes the one its kernels know."""
     dims: int
     base: float
     factor: Optional[float] = None
     original: float = 0.0
     fast: float = 0.0
     slow: float = 0.0
+    pairing: str = "half"
     kind: str = "yarn_rope"
 
 
@@ -94,7 +96,14 @@ class BiasedAttentionSpec:
     `value_mix` names a scalar lambda: the layer caches and uses (1 - lambda) v + lambda v_src, v_src
     being the values that the layer with `value_source` made of the same token (that layer's own values
     stay unmixed).  `head_gate` (n_heads, hidden): head h's output is multiplied by sigmoid of row h
-    applied to the mixer's input."""
+    applied to the mixer's input.
+
+    Further options, each off by default.  `v_proj` None: the values are the keys as projected (before rotation
+    and norm; v_dim = dim).  `rotation`: a rotary spec with adjacent pairing, applied to queries and keys before
+    their norms.  `unit_norm`: queries and keys are divided by their root mean square per head without a weight
+    (instead of `q_norm` / `k_norm`).  `q_temp` = (coef, every): queries are multiplied by 1 + coef ln(floor((p +
+    1) / every) + 1) at position p.  `slopes`: one number a head, slope * distance is subtracted from a score.
+    `sink` (n_heads,): exp(sink_h) joins the denominator of head h's softmax, without a key or a value."""
     hidden: int
     n_heads: int
     n_kv_heads: int
@@ -104,7 +113,7 @@ class BiasedAttentionSpec:
     eps: float
     q_proj: str                      # (n_heads * dim, hidden)
     k_proj: str                      # (n_kv_heads * dim, hidden)
-    v_proj: str                      # (n_kv_heads * v_dim, hidden)
+    v_proj: Optional[str]            # (n_kv_heads * v_dim, hidden)
     o_proj: str                      # (hidden, n_heads * v_dim)
     q_norm: Optional[str] = None     # (dim,)
     k_norm: Optional[str] = None     # (dim,)
@@ -113,6 +122,11 @@ class BiasedAttentionSpec:
     value_mix: Optional[str] = None  # scalar tensor
     value_source: bool = False
     window: Optional[int] = None
+    rotation: Any = None
+    unit_norm: bool = False
+    q_temp: Optional[tuple] = None   # (coef, every)
+    slopes: Optional[tuple] = None   # one a head
+    sink: Optional[str] = None       # (n_heads,)
     kind: str = "biased_attention"
 
 
@@ -168,6 +182,50 @@ class LightningAttentionSpec:
 
 
 @dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule: q, k = W h (n_qk_heads x dim), v = W_v h (n_heads x v_dim); each passes a causal
+    convolution over time per channel (`conv` taps, weights `<projection>.conv`-like tensors (channels, taps), the
+    last tap on the current token) and silu; q and k become unit vectors per head (x / sqrt(sum x^2 + unit_eps)),
+    q times dim^(-1/2); beta = sigmoid(W_b h) and decay g = exp(-exp(a_log) softplus(W_a h + dt_bias)), one a
+    head; per head S <- g S, u = beta (v - S^T k), S <- S + k u^T, o = S^T q (float32 state per request); out =
+    W_o (rmsnorm_per_head(o) * out_norm * silu(W_g h)).  Head h reads q and k of head h / (n_heads / n_qk_heads)."""
+    hidden: int
+    n_heads: int
+    n_qk_heads: int
+    dim: int
+    v_dim: int
+    conv: int
+    eps: float
+    q_proj: str                      # (n_qk_heads * dim, hidden)
+    k_proj: str
+    v_proj: str                      # (n_heads * v_dim, hidden)
+    q_conv: str                      # (n_qk_heads * dim, conv)
+    k_conv: str
+    v_conv: str                      # (n_heads * v_dim, conv)
+    beta_proj: str                   # (n_heads, hidden)
+    decay_proj: str                  # (n_heads, hidden)
+    a_log: str                       # (n_heads,)
+    dt_bias: str                     # (n_heads,)
+    gate_proj: str                   # (n_heads * v_dim, hidden)
+    out_norm: str                    # (v_dim,)
+    o_proj: str                      # (hidden, n_heads * v_dim)
+    unit_eps: float = 1e-6
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Several mixers side by side on the same input: the result is the mean of their outputs, each first
+    RMS-normed over the model width with a weight of its own (`out_norms`, one tensor name a branch).  At most
+    one branch keeps a paged cache and at most one a per-request state."""
+    hidden: int
+    branches: tuple                  # of mixer specs
+    out_norms: tuple                 # of tensor names, shape (hidden,)
+    eps: float
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
 class DenseFFSpec:
     """W_down act(W_up h + b_up) + b_down; `activation` "relu2" is the square of max(., 0).  The
     biases are optional tensors."""
@@ -201,6 +259,8 @@ class RoutedFFSpec:
     """A mixture of `n_experts` gated feed-forwards (each as SwiGLUSpec describes, `intermediate` wide) of
     which a token uses `top`.  Scores s = sigmoid(W_router h) in float32; the experts with the largest
     s + correction are chosen; their outputs are summed with weights s * route_scale (not renormalised).
+    `scoring` "softmax_chosen": the logits z = W_router h + router_bias choose, and the weights are the softmax
+    over the chosen logits alone.
     Tensor names of expert e are the patterns with {e} filled in.  `shared`: a SwiGLUSpec that every token
     runs through, added after multiplication by sigmoid(W_shared_gate h) where `shared_gate` is given."""
     hidden: int
@@ -218,17 +278,21 @@ class RoutedFFSpec:
     up_shift: float = 0.0
     shared: Any = None
     shared_gate: Optional[str] = None  # (1, hidden)
+    router_bias: Optional[str] = None  # (n_experts,)
+    scoring: str = "sigmoid"
     kind: str = "routed_ff"
 
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
     """Token table: row `id` of `weight` (vocab, dim) starts the residual stream, multiplied by
-    `scale` if one is given (the reference's Llama has none, crates/model/src/llama.rs:256-262)."""
+    `scale` if one is given (the reference's Llama has none, crates/model/src/llama.rs:256-262), then
+    normed where `norm` (an RMSNormSpec) is given."""
     vocab_size: int
     dim: int
     weight: str
     scale: Optional[float] = None
+    norm: Any = None
     kind: str = "embedding"
 
 
@@ -253,7 +317,9 @@ class LayerSpec:
     with norm2, feed_forward, post_norm2, scale2; `feed_forward` None leaves the second sublayer out
     (norm2, post_norm2 and scale2 are then None too).  arrangement "outnorm": the sublayers read the
     stream itself and only their results are normed, x += residual_mult * norm1(mixer(x)), then x +=
-    residual_mult * norm2(feed_forward(x)), the second line only with a feed-forward."""
+    residual_mult * norm2(feed_forward(x)), the second line only with a feed-forward.  arrangement "postnorm": the
+    sum is normed, x = norm1(stream_mult * x + mixer(x)), then x = norm2(stream_mult * x + feed_forward(x)), the
+    sublayers reading x itself and the second line only with a feed-forward."""
     norm1: Any
     mixer: Any
     norm2: Any
@@ -264,6 +330,7 @@ class LayerSpec:
     scale1: Optional[str] = None     # tensor name, shape (hidden,): per-channel scale of the sublayer's result
     scale2: Optional[str] = None
     residual_mult: float = 1.0
+    stream_mult: float = 1.0
 
 
 @dataclass(frozen=True)

@@ -20,8 +20,9 @@ from ..config.registry import lookup_architecture
 from .safetensors_io import save_file
 
 _STORE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
-# kinds other than "matrix" and "norm": "offset" (weights stored around zero, biases), "gain" (free scalars)
-_STD = {"offset": 0.1, "gain": 1.0}
+# kinds other than "matrix" and "norm": "offset" (weights stored around zero, biases), "gain" (free scalars),
+# "taps" (short convolutions over time)
+_STD = {"offset": 0.1, "gain": 1.0, "taps": 0.5}
 
 
 def _tensor_key(seed: int, name: str) -> list[int]:
