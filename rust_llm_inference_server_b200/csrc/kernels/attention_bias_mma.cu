@@ -1,6 +1,7 @@
 // Tensor-core kernels (bfloat16) for the attention that attention_bias.cu describes: normed queries and
 // keys, score = scale * q . k + bias[min(distance, n_dist - 1), head], keys of width D and values of
-// width DV, a gate on every head's result.  mma.sync m16n8k16 with float32 sums; keys and values reach
+// width DV, a gate on every head's result; optionally slope_h * distance is subtracted from a score and
+// exp(sink_h) joins the denominator of head h's softmax.  mma.sync m16n8k16 with float32 sums; keys and values reach
 // shared memory by 16-byte asynchronous copies, two or three stages deep, in tiles of 64 keys; rows padded by 8
 // elements so that ldmatrix is free of bank conflicts; softmax in float32 in units of log2(e).
 //
@@ -84,7 +85,7 @@ __global__ __launch_bounds__(THREADS, (D + DV <= 128) ? 4 : 3) void attn_bias_pr
     bf16* __restrict__ out, const float* __restrict__ bias, int n_dist, const bf16* __restrict__ gate,
     long long gate_stride, const int* __restrict__ tiles, const int* __restrict__ cu_seqlens,
     const int* __restrict__ ctx_lens, const int* __restrict__ block_tables, int max_blocks, int nh, int nkv,
-    int page_size, float scale, int window) {
+    int page_size, float scale, int window, const float* __restrict__ sinks, const float* __restrict__ slopes) {
     pdl_wait();
     constexpr int SK = D + 8, SV = DV + 8;
     constexpr int KS = D / 16, ND = DV / 8;
@@ -131,6 +132,7 @@ __global__ __launch_bounds__(THREADS, (D + DV <= 128) ? 4 : 3) void attn_bias_pr
     const bf16* kbase = k_cache + (size_t)kvh * page_size * D;
     const bf16* vbase = v_cache + (size_t)kvh * page_size * DV;
     const float far_bias = bias != nullptr ? bias[(size_t)(n_dist - 1) * nh + head] * LOG2E : 0.f;
+    const float slope_l2 = slopes != nullptr ? slopes[head] * LOG2E : 0.f;
 
     auto issue = [&](int kt, int stage) {
         bf16* ks_ = sbase + (size_t)stage * Stage<D, DV>::ELEMS;
@@ -182,7 +184,7 @@ __global__ __launch_bounds__(THREADS, (D + DV <= 128) ? 4 : 3) void attn_bias_pr
         const bool edge = (kt + 1) * BN - 1 > start_pos + t0 + warp * 16 || window > 0;
         const bool near = bias != nullptr && start_pos + t0 - (kt * BN + BN - 1) < n_dist - 1;
         float mx0 = -INFINITY, mx1 = -INFINITY;
-        if (!edge && !near) {
+        if (!edge && !near && slopes == nullptr) {
             // most tiles of a long prompt: every key is seen by every row, and all share the table's last row
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt)
@@ -203,8 +205,10 @@ __global__ __launch_bounds__(THREADS, (D + DV <= 128) ? 4 : 3) void attn_bias_pr
                     const int j = nt * 8 + 2 * c + e;
                     float s0 = fmaf(sacc[nt][e], scale_log2, near ? bs[r0 + BN - 1 - j] : far_bias);
                     float s1 = fmaf(sacc[nt][2 + e], scale_log2, near ? bs[r1 + BN - 1 - j] : far_bias);
+                    const int key = kt * BN + j;
+                    s0 = fmaf(slope_l2, (float)(key - pos0), s0);       // minus slope * distance
+                    s1 = fmaf(slope_l2, (float)(key - pos1), s1);
                     if (edge) {
-                        const int key = kt * BN + j;
                         if (!(key <= pos0 && key >= lo0)) s0 = -INFINITY;
                         if (!(key <= pos1 && key >= lo1)) s1 = -INFINITY;
                     }
@@ -267,6 +271,12 @@ __global__ __launch_bounds__(THREADS, (D + DV <= 128) ? 4 : 3) void attn_bias_pr
         stage ^= 1;
     }
 
+    if (sinks != nullptr) {
+        // one more term of the denominator, without a key or a value (a sink far above every score gives inf, and 0)
+        const float sink_l2 = sinks[head] * LOG2E;
+        l_run[0] += ex2(sink_l2 - m_run[0]);
+        l_run[1] += ex2(sink_l2 - m_run[1]);
+    }
     float inv0 = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f;
     float inv1 = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
     if (gate != nullptr) {
@@ -295,7 +305,8 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
     bf16* __restrict__ out, float* __restrict__ partial, const float* __restrict__ bias, int n_dist,
     const bf16* __restrict__ gate, long long gate_stride, const int* __restrict__ dec_rows,
     const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens, const int* __restrict__ block_tables,
-    int max_blocks, int nh, int nkv, int page_size, float scale, int window, int pieces) {
+    int max_blocks, int nh, int nkv, int page_size, float scale, int window, int pieces,
+    const float* __restrict__ sinks, const float* __restrict__ slopes) {
     pdl_wait();
     constexpr int SK = D + 8, SV = DV + 8;
     constexpr int KS = D / 16, ND = DV / 8;
@@ -338,6 +349,8 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
     const float* brow1 = bias != nullptr ? bias + (rv1 ? h1 : 0) : nullptr;
     const float far0 = bias != nullptr ? brow0[(size_t)(n_dist - 1) * nh] * LOG2E : 0.f;
     const float far1 = bias != nullptr ? brow1[(size_t)(n_dist - 1) * nh] * LOG2E : 0.f;
+    const float slope0 = slopes != nullptr && rv0 ? slopes[h0] * LOG2E : 0.f;
+    const float slope1 = slopes != nullptr && rv1 ? slopes[h1] * LOG2E : 0.f;
 
     auto issue = [&](int kt, int stage) {
         bf16* ks_ = sbase + (size_t)stage * Stage<D, DV>::ELEMS;
@@ -395,8 +408,9 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
                         b0 = brow0[at] * LOG2E;
                         b1 = brow1[at] * LOG2E;
                     }
-                    const float s0 = seen ? fmaf(sacc[nt][e], scale_log2, b0) : -INFINITY;
-                    const float s1 = seen ? fmaf(sacc[nt][2 + e], scale_log2, b1) : -INFINITY;
+                    const float dist = (float)(key - pos);                   // minus the distance
+                    const float s0 = seen ? fmaf(slope0, dist, fmaf(sacc[nt][e], scale_log2, b0)) : -INFINITY;
+                    const float s1 = seen ? fmaf(slope1, dist, fmaf(sacc[nt][2 + e], scale_log2, b1)) : -INFINITY;
                     sacc[nt][e] = s0;
                     sacc[nt][2 + e] = s1;
                     mx0 = fmaxf(mx0, s0);
@@ -487,6 +501,7 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
         }
         const int head = kvh * nrep + r;
         if (pieces == 1) {
+            if (sinks != nullptr) l += exp2f(sinks[head] * LOG2E - m);
             float inv = l > 0.f ? 1.0f / l : 0.f;
             if (gate != nullptr) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * gate_stride + head])));
             out[((size_t)row * nh + head) * DV + col] = __float2bfloat16_rn(o * inv);
@@ -501,7 +516,7 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
 // Pieces of a context into one result: one warp a (token, head).
 __global__ __launch_bounds__(128) void attn_bias_decode_merge_kernel(
     const float* __restrict__ partial, bf16* __restrict__ out, const bf16* __restrict__ gate, long long gate_stride,
-    const int* __restrict__ dec_rows, int n_units, int nh, int dv, int pieces) {
+    const int* __restrict__ dec_rows, int n_units, int nh, int dv, int pieces, const float* __restrict__ sinks) {
     pdl_wait_and_trigger();
     const int unit = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (unit >= n_units) return;
@@ -516,6 +531,7 @@ __global__ __launch_bounds__(128) void attn_bias_decode_merge_kernel(
         const float ms = p[(size_t)s * mw + dv];
         l = fmaf(p[(size_t)s * mw + dv + 1], ms == -INFINITY ? 0.f : exp2f(ms - m), l);
     }
+    if (sinks != nullptr) l += exp2f(sinks[head] * LOG2E - m);
     float inv = l > 0.f ? 1.0f / l : 0.f;
     if (gate != nullptr) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * gate_stride + head])));
     for (int col = lane; col < dv; col += 32) {
@@ -556,7 +572,8 @@ extern "C" int rlis_attention_bias_prefill(const void* q, const void* k_cache, c
                                            const float* bias, int n_dist, const void* gate, long long gate_stride,
                                            const int* tiles, int n_tiles, const int* cu_seqlens, const int* ctx_lens,
                                            const int* block_tables, int max_blocks, int nh, int nkv, int d, int dv,
-                                           int page_size, float scale, int window, cudaStream_t stream) {
+                                           int page_size, float scale, int window, const float* sinks,
+                                           const float* slopes, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!sizes_taken(d, dv) || nkv <= 0 || nh % nkv != 0 || n_tiles > 65535 || (bias != nullptr && n_dist <= 0))
         return RLIS_ERR_UNSUPPORTED;
@@ -564,19 +581,20 @@ extern "C" int rlis_attention_bias_prefill(const void* q, const void* k_cache, c
     dim3 grid(nh, n_tiles);
 #define RLIS_AB_PF(D_, DV_) rlis_launch(attn_bias_prefill_kernel<D_, DV_>, grid, THREADS, smem_bytes<D_, DV_>(), stream, \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, bias, n_dist, (const bf16*)gate,      \
-        gate_stride, tiles, cu_seqlens, ctx_lens, block_tables, max_blocks, nh, nkv, page_size, scale, window)
+        gate_stride, tiles, cu_seqlens, ctx_lens, block_tables, max_blocks, nh, nkv, page_size, scale, window,        \
+        sinks, slopes)
     RLIS_AB_DISPATCH(RLIS_AB_PF)
 #undef RLIS_AB_PF
     return RLIS_LAUNCH_CHECK();
 }
 
-// partial: float32, at least n_dec * nh * pieces * (dv + 2) elements when pieces > 1.
+// partial: float32, at least n_dec * nh * pieces * (dv + 2) elements when pieces > 1.  sinks, slopes: float32 [nh] or null.
 extern "C" int rlis_attention_bias_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
                                           float* partial, const float* bias, int n_dist, const void* gate,
                                           long long gate_stride, const int* dec_rows, const int* dec_seqs,
                                           const int* ctx_lens, const int* block_tables, int max_blocks, int n_dec,
                                           int nh, int nkv, int d, int dv, int page_size, float scale, int window,
-                                          int pieces, cudaStream_t stream) {
+                                          int pieces, const float* sinks, const float* slopes, cudaStream_t stream) {
     if (n_dec <= 0) return 0;
     if (!sizes_taken(d, dv) || nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || pieces < 1 || pieces > 65535 ||
         n_dec > 65535 || (bias != nullptr && n_dist <= 0) || (pieces > 1 && partial == nullptr))
@@ -586,13 +604,13 @@ extern "C" int rlis_attention_bias_decode(const void* q, const void* k_cache, co
 #define RLIS_AB_DEC(D_, DV_) rlis_launch(attn_bias_decode_kernel<D_, DV_>, grid, THREADS, decode_smem_bytes<D_, DV_>(), stream, \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, bias, n_dist,                 \
         (const bf16*)gate, gate_stride, dec_rows, dec_seqs, ctx_lens, block_tables, max_blocks, nh, nkv, page_size,   \
-        scale, window, pieces)
+        scale, window, pieces, sinks, slopes)
     RLIS_AB_DISPATCH(RLIS_AB_DEC)
 #undef RLIS_AB_DEC
     int err = RLIS_LAUNCH_CHECK();
     if (err != 0 || pieces == 1) return err;
     const int units = n_dec * nh;
     rlis_launch(attn_bias_decode_merge_kernel, (units + 3) / 4, 128, 0, stream, (const float*)partial, (bf16*)out,
-                (const bf16*)gate, gate_stride, dec_rows, units, nh, dv, pieces);
+                (const bf16*)gate, gate_stride, dec_rows, units, nh, dv, pieces, sinks);
     return RLIS_LAUNCH_CHECK();
 }

@@ -1133,11 +1133,10 @@ def _biased_mma_sizes(dim: int, v_dim: int) -> bool:
     return bool(lib().rlis_attention_bias_mma_takes(dim, v_dim))
 
 
-def biased_attention_takes_mma(dtype, n_heads: int, n_kv_heads: int, dim: int, v_dim: int, sinks: bool = False,
-                               slopes: bool = False) -> bool:
-    """Whether the tensor-core kernels for attention with a bias by distance exist for these sizes and options."""
+def biased_attention_takes_mma(dtype, n_heads: int, n_kv_heads: int, dim: int, v_dim: int) -> bool:
+    """Whether the tensor-core kernels for attention with a bias by distance exist for these sizes."""
     return bool(BIASED_MMA and dtype == torch.bfloat16 and n_heads % n_kv_heads == 0
-                and _biased_mma_sizes(int(dim), int(v_dim)) and not sinks and not slopes)
+                and _biased_mma_sizes(int(dim), int(v_dim)))
 
 
 @functools.lru_cache(maxsize=4096)
@@ -1185,7 +1184,7 @@ def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_h
     sp = sinks.data_ptr() if sinks is not None else None
     lp = slopes.data_ptr() if slopes is not None else None
     tables = step.block_tables[group]
-    fast = biased_attention_takes_mma(q.dtype, n_heads, n_kv_heads, dim, v_dim, sinks is not None, slopes is not None)
+    fast = biased_attention_takes_mma(q.dtype, n_heads, n_kv_heads, dim, v_dim)
     n_dec = getattr(step, "n_decode", 0) if fast and n_heads // n_kv_heads <= 16 else 0
     n_tiles = getattr(step, "n_prefill_tiles", 0) if fast else 0
     if n_dec:
@@ -1195,14 +1194,14 @@ def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_h
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
             scratch.data_ptr() if scratch is not None else None, bp, n_dist, gp, gs, step.dec_rows.data_ptr(),
             step.dec_seqs.data_ptr(), step.ctx_lens.data_ptr(), tables.data_ptr(), tables.shape[1], n_dec, n_heads,
-            n_kv_heads, dim, v_dim, page_size, float(scale), int(window), pieces, _stream()), "attention_bias_decode")
+            n_kv_heads, dim, v_dim, page_size, float(scale), int(window), pieces, sp, lp, _stream()), "attention_bias_decode")
         _count("attention_bias.decode.mma" + (".split" if pieces > 1 else ""))
     if n_tiles:
         check(lib().rlis_attention_bias_prefill(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), bp, n_dist, gp, gs,
             step.prefill_tiles.data_ptr(), n_tiles, step.cu_seqlens.data_ptr(), step.ctx_lens.data_ptr(),
             tables.data_ptr(), tables.shape[1], n_heads, n_kv_heads, dim, v_dim, page_size, float(scale), int(window),
-            _stream()), "attention_bias_prefill")
+            sp, lp, _stream()), "attention_bias_prefill")
         _count("attention_bias.prefill.mma")
     # what the tensor-core kernels did not take: nothing, the portions only, the single tokens only, or everything
     rows, n_rows = None, T

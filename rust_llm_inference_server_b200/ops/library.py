@@ -46,8 +46,8 @@ SIGNATURES = {
     "rlis_qk_norm_store": [P, LL, I, I, I, P, P, F, P, LL, F, P, P, P, P, I, I, I, I, I, I, P, I, F, P, F, I, I, P],
     "rlis_attention_bias": [P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, P],
     "rlis_attention_bias_mma_takes": [I, I],
-    "rlis_attention_bias_prefill": [P, P, P, P, P, I, P, LL, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
-    "rlis_attention_bias_decode": [P, P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
+    "rlis_attention_bias_prefill": [P, P, P, P, P, I, P, LL, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P, P],
+    "rlis_attention_bias_decode": [P, P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
     "rlis_moe_route": [P, P, P, P, P, P, I, I, I, I, F, P, I, I, P],
     "rlis_moe_align": [P, P, P, P, I, I, I, I, P],
     "rlis_moe_gemm": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, LL, I, I, P],

@@ -144,8 +144,7 @@ class BiasedAttention(Mixer):
 
     def _fast(self) -> bool:
         s = self.spec
-        return ops.biased_attention_takes_mma(self.dtype, s.n_heads, s.n_kv_heads, s.dim, s.v_dim,
-                                              sinks=s.sink is not None, slopes=s.slopes is not None)
+        return ops.biased_attention_takes_mma(self.dtype, s.n_heads, s.n_kv_heads, s.dim, s.v_dim)
 
     @property
     def prefill_tile(self):
