@@ -742,6 +742,135 @@ def workload_gavodra(args, torch, np) -> dict:
     return out
 
 
+def lanirax_config(width: int, vocab: int = 32000) -> dict:
+    """Four Lanirax layers at a real model's proportions.  Parallel layers: a window of 1,024 over heads of 64
+    in groups of four (keys double as values, three quarters of a head rotated) beside a gated delta rule with heads of
+    128 x 128, two value heads a query/key head, four taps.  Slope layers: heads of 64 in groups of four.
+    Every layer routes to 4 of 32 experts of half a width (2 widths of feed-forward a token)."""
+    H = width // 64
+    rot = {"dims": 48, "base": 10000.0, "scaling": {"factor": 4.0, "original": 8192, "fast": 16.0, "slow": 2.0}}
+    left = {"heads": H, "kv_heads": max(1, H // 4), "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024}, "rot": rot}
+    right = {"heads": width // 128, "kv_heads": max(1, width // 256), "dim": 128, "vdim": 128, "conv": 4}
+    slope = {"heads": H, "kv_heads": max(1, H // 4), "dim": 64, "vdim": 64, "scale": 0.125, "q_temp": {"coef": 0.3, "every": 1024}}
+    moe = {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 32, "top": 4}}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": moe}
+    att = {"type": "attention", "mixer": slope, "mlp": moe}
+    return {"architecture": "Lanirax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "postln_alpha": 2.0,
+            "layers": [par, att, par, att]}
+
+
+def lanirax_kernel_rooflines(width: int, B: int, ctx: int, T: int, pk: dict, torch, np) -> dict:
+    """The kernels that Lanirax adds or extends, alone, at the sizes of `lanirax_config(width)`, each beside
+    the like kernel of the closest models: {name: {"us", "ideal_us", "frac"}}.  Ideal: bytes that must move over
+    the measured copy bandwidth (single tokens, norms), FLOPs over the measured bfloat16 GEMM rate (attention
+    over prompts), or float32 FMAs over the FFMA rate of the SMs at their maximum clock (the recurrences over
+    prompts, float32 by design)."""
+    from rust_llm_inference_server_b200 import ops
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ffma = sms * 128 * 2 * pk.get("sm_max_mhz", 1965.0) * 1e6
+    page, nh, nkv, hd, window = 16, width // 64, max(1, width // 256), 64, 1024
+    rh, rqk, rd, taps = width // 128, max(1, width // 256), 128, 4
+    bf, out = torch.bfloat16, {}
+    rnd = lambda *shape: torch.randn(*shape, device="cuda") * 0.3
+
+    def row(name, us, ideal_s):
+        out[name] = {"us": round(us, 1), "ideal_us": round(ideal_s * 1e6, 1), "frac": round(ideal_s * 1e6 / us, 3)}
+
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / nh) for h in range(nh)], device="cuda")
+    sinks, bias = rnd(nh).contiguous(), rnd(129, nh).contiguous()
+    for kind, reqs in (("decode", [(ctx - 1, 1)] * B), ("prefill", [(0, T)])):
+        st = _KernelStep(reqs, page, torch, np)
+        st.n_prefill_tokens = st.n_prefill_tokens if kind == "prefill" else 0
+        n = st.n_tokens
+        keys = B * ctx if kind == "decode" else T * (T + 1) // 2
+        seen = B * min(ctx, window) if kind == "decode" else sum(min(i + 1, window) for i in range(T))
+        kc, vc, q = rnd(st.n_pages, nkv, page, hd).to(bf), rnd(st.n_pages, nkv, page, hd).to(bf), rnd(n, nh * hd).to(bf)
+        gate = rnd(n, nh + 8).to(bf)[:, :nh]
+        o = torch.empty_like(q)
+        attn = lambda k: k * nkv * hd * 2 * 2 / hbm if kind == "decode" else 2 * nh * k * 2 * hd / tf
+        us = _graph_time_us(lambda: ops.attention_biased(q, kc, vc, o, None, None, st, 0, nh, nkv, hd, hd, page, 0.125, 0,
+                                                         slopes=slopes), torch)
+        row(f"slope_attention_{kind}", us, attn(keys))
+        us = _graph_time_us(lambda: ops.attention_biased(q, kc, vc, o, None, None, st, 0, nh, nkv, hd, hd, page, 0.125, window,
+                                                         sinks=sinks), torch)
+        row(f"window_sink_attention_{kind}", us, attn(seen))
+        us = _graph_time_us(lambda: ops.attention_biased(q, kc, vc, o, bias, gate, st, 0, nh, nkv, hd, hd, page, 0.125, 0), torch)
+        row(f"table_bias_attention_{kind}", us, attn(keys))
+        # the recurrences: the gated delta rule (convolutions, unit norms and gates in its first kernel) beside the
+        # decayed linear attention at the same head sizes
+        C = 2 * rqk * rd + rh * rd
+        proj = rnd(n, C + rh * rd + 2 * rh + (-(2 * rh) % 8)).to(bf)
+        conv_w, a_log, dt_bias = rnd(C, taps).contiguous(), rnd(rh).contiguous(), rnd(rh).contiguous()
+        state = torch.zeros(len(reqs), ops.gated_delta_state_floats(rh, rqk, rd, rd, taps), device="cuda")
+        o3 = torch.empty(n, rh * rd, device="cuda")
+        us = _graph_time_us(lambda: ops.gated_delta(proj, 0, C + rh * rd, C + rh * rd + rh, conv_w, a_log, dt_bias, state, o3, st,
+                                                    rh, rqk, rd, rd, taps, 1e-6, rd ** -0.5), torch)
+        row(f"gated_delta_{kind}", us, B * rh * rd * rd * 4 * 2 / hbm if kind == "decode" else 3 * 2 * T * rh * rd * rd / ffma)
+        proj2 = rnd(n, 3 * rh * rd).to(bf)
+        state2, decay = torch.zeros(len(reqs), rh, rd, rd, device="cuda"), torch.full((rh,), 0.97, device="cuda")
+        us = _graph_time_us(lambda: ops.lightning_scan(proj2, 0, rh * rd, 2 * rh * rd, o3, state2, decay, st, rh, rd, rd), torch)
+        row(f"decayed_linear_attention_{kind}", us, B * rh * rd * rd * 4 * 2 / hbm if kind == "decode" else 2 * 2 * T * rh * rd * rd / ffma)
+        # the normed sum of stream and two normed branches beside the norm of one sublayer's result
+        resid, wv = rnd(n, width).contiguous(), torch.ones(width, device="cuda")
+        a, b, y = rnd(n, width).to(bf), rnd(n, width).to(bf), torch.empty(n, width, dtype=bf, device="cuda")
+        us = _graph_time_us(lambda: ops.sum_norm(resid, 2.5, [(a, wv, 0.5), (b, wv, 0.5)], wv, 1e-6, out=y, eps_branch=1e-6), torch)
+        row(f"sum_norm_two_branches_{kind}", us, n * width * (4 + 4 + 2 + 2 + 2) / hbm)
+        us = _graph_time_us(lambda: ops.post_norm_residual(a, resid, wv, 1e-6, out=y, mult=0.5), torch)
+        row(f"post_norm_residual_{kind}", us, n * width * (4 + 4 + 2 + 2) / hbm)
+    return out
+
+
+def workload_lanirax(args, torch, np) -> dict:
+    """Prefill (one 2,048-token prompt) and decode (batch 8, context 4,096) of four Lanirax layers at two
+    widths beside four Gavodra layers (the closest model: the same attention kernels and routed feed-forwards) and
+    four Llama layers of the same width, random bfloat16 weights; then the stages of one step by CUDA-event spans
+    (eager launches), and the kernels alone, replayed from CUDA graphs, against their rooflines."""
+    from rust_llm_inference_server_b200 import LLM
+    from rust_llm_inference_server_b200.ops import profile
+    pk, pk_src = peaks()
+    B, ctx, page, T = args.batch, args.context, 16, PREFILL_TOKENS
+    steps = min(args.steps, 64)
+    out = {"workload": "lanirax", "metric": "prefill and decode tokens/s of four layers, Lanirax beside Gavodra and Llama at equal width",
+           "unit": "tokens/s", "impl": "ours", "dtype": "bf16", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+           "data": "synthetic: uniform-random token ids, random-init weights (device generator)",
+           "config": {"global_batch": B, "seq_len": ctx, "prefill_tokens": T, "page_size": page, "layers": 4},
+           "peaks": dict(pk, source=pk_src), "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for width in (1024, 2048):
+        row = {}
+        for name, cfg in (("lanirax", lanirax_config(width)), ("gavodra", gavodra_config(width)), ("llama", llama_config_like(width))):
+            llm = LLM.from_random(cfg, 8, dtype="bfloat16", on_device=True, max_seq_len=ctx + page,
+                                  num_blocks=B * (ctx + page) // page + 64, block_size=page, max_num_seqs=B,
+                                  max_batched_tokens=max(2048, B), prefix_caching=False)
+            pre = prefill_run(llm, T, 5, 3, torch, np)
+            ms, launches = decode_run(llm, B, steps, args.warmup, ctx, torch)
+            profile.enable(True)
+            prefill_run(llm, T, 3, 2, torch, np)
+            profile.take_report()
+            prefill_run(llm, T, 3, 0, torch, np)
+            pre_stages = {k: round(v[0] / 3 * 1e3, 1) for k, v in profile.take_report().items()}
+            decode_run(llm, B, 8, 4, ctx, torch, fill=False)
+            dec_stages = {k: round(v[0] / 8 * 1e3, 1) for k, v in profile.take_report().items()}
+            profile.enable(False)
+            row[name] = {"prefill_tokens_per_s": round(T / (pre / 1e3), 1), "prefill_ms": round(pre, 3),
+                         "decode_tokens_per_s": round(B / (ms / 1e3), 1), "decode_ms_per_step": round(ms, 4),
+                         "launches_per_decode_step": launches,
+                         "weight_bytes": int(sum(p.numel() * p.element_size() for p in _model_tensors(llm.model))),
+                         "prefill_stage_us": pre_stages, "decode_stage_us": dec_stages}
+            del llm
+            torch.cuda.empty_cache()
+        row["rooflines"] = lanirax_kernel_rooflines(width, B, ctx, T, pk, torch, np)
+        out["sizes"][f"width{width}"] = row
+    out["clocks"] = clocks.stop()
+    head = out["sizes"]["width2048"]["lanirax"]
+    out["value"] = head["decode_tokens_per_s"]
+    out["ms_per_step"] = head["decode_ms_per_step"]
+    out["gpu_launches"] = int(round(head["launches_per_decode_step"] * steps))
+    return out
+
+
 def _model_tensors(model):
     seen = {}
     for part in model.parts():
@@ -772,7 +901,7 @@ def print_timeline(records: list) -> None:
 
 
 WORKLOADS = {"3b": workload_3b, "8b": workload_8b, "1b-fp32": workload_1b_fp32, "lasapel": workload_lasapel,
-             "gavodra": workload_gavodra}
+             "gavodra": workload_gavodra, "lanirax": workload_lanirax}
 
 
 def main() -> int:

@@ -13,6 +13,34 @@ import math
 import numpy as np
 
 
+_coarse = [lambda x: x]
+
+
+class coarse_products:
+    """Within this context every matrix product takes its inputs, and leaves its result, through `fn` (the
+    rounding of a narrower number type), and so do the queries and keys that attention keeps; everything else
+    stays float64.  It models what rounding alone does to the logits: the tests take their tolerance for a
+    narrow type from it."""
+
+    def __init__(self, fn):
+        self.fn = fn
+
+    def __enter__(self):
+        _coarse.append(self.fn)
+
+    def __exit__(self, *exc):
+        _coarse.pop()
+
+
+def kept(x):
+    return _coarse[-1](x)
+
+
+def linear(h, weight, exact_result=False):
+    y = kept(h) @ weight.T
+    return y if exact_result else kept(y)
+
+
 def rms_unit(x, eps):
     """x divided by its root mean square over the last axis (eps under the root)."""
     return x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps)
@@ -93,15 +121,15 @@ def window_sink_mixer(h, w, p, m, eps):
     root mean square, a window and a sink."""
     T = h.shape[0]
     H, G, d = m["heads"], m["kv_heads"], m["dim"]
-    q = (h @ w[p + "q"].T).reshape(T, H, d)
-    k = (h @ w[p + "k"].T).reshape(T, G, d)
+    q = linear(h, w[p + "q"]).reshape(T, H, d)
+    k = linear(h, w[p + "k"]).reshape(T, G, d)
     v = k.copy()
     freqs, mag = blended_frequencies(m["rot"])
     pos = np.arange(T, dtype=np.float64)
-    q = rms_unit(rotate_adjacent_pairs(q, pos, freqs, mag), eps)
-    k = rms_unit(rotate_adjacent_pairs(k, pos, freqs, mag), eps)
+    q = kept(rms_unit(rotate_adjacent_pairs(q, pos, freqs, mag), eps))
+    k = kept(rms_unit(rotate_adjacent_pairs(k, pos, freqs, mag), eps))
     o = masked_attention(q, k, v, m["scale"], window=m["mask"]["size"], sinks=w[p + "sink"])
-    return o.reshape(T, -1) @ w[p + "o"].T
+    return linear(o.reshape(T, -1), w[p + "o"])
 
 
 def temperature(T, q_temp):
@@ -118,12 +146,13 @@ def slope_mixer(h, w, p, m, eps):
     in steps with the position, and a penalty linear in the distance."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = rms_unit((h @ w[p + "q"].T).reshape(T, H, d), eps) * w[p + "q.norm"]
-    k = rms_unit((h @ w[p + "k"].T).reshape(T, G, d), eps) * w[p + "k.norm"]
-    v = (h @ w[p + "v"].T).reshape(T, G, dv)
-    q = q * temperature(T, m["q_temp"])[:, None, None]
-    o = masked_attention(q, k, v, m["scale"], slopes=head_slopes(H))
-    return o.reshape(T, -1) @ w[p + "o"].T
+    q = rms_unit(linear(h, w[p + "q"]).reshape(T, H, d), eps) * w[p + "q.norm"]
+    k = rms_unit(linear(h, w[p + "k"]).reshape(T, G, d), eps) * w[p + "k.norm"]
+    v = linear(h, w[p + "v"]).reshape(T, G, dv)
+    if m.get("q_temp") is not None:
+        q = q * temperature(T, m["q_temp"])[:, None, None]
+    o = masked_attention(kept(q), kept(k), v, m["scale"], slopes=head_slopes(H))
+    return linear(o.reshape(T, -1), w[p + "o"])
 
 
 # ---- the recurrent branch -------------------------------------------------------------------------
@@ -157,19 +186,19 @@ def delta_rule(q, k, v, beta, decay):
 def delta_mixer(h, w, p, m, eps):
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = silu(short_conv(h @ w[p + "q"].T, w[p + "q.conv"])).reshape(T, G, d)
-    k = silu(short_conv(h @ w[p + "k"].T, w[p + "k.conv"])).reshape(T, G, d)
-    v = silu(short_conv(h @ w[p + "v"].T, w[p + "v.conv"])).reshape(T, H, dv)
+    q = silu(short_conv(linear(h, w[p + "q"]), w[p + "q.conv"])).reshape(T, G, d)
+    k = silu(short_conv(linear(h, w[p + "k"]), w[p + "k.conv"])).reshape(T, G, d)
+    v = silu(short_conv(linear(h, w[p + "v"]), w[p + "v.conv"])).reshape(T, H, dv)
     q = q / np.sqrt((q * q).sum(-1, keepdims=True) + 1e-6) * d ** -0.5
     k = k / np.sqrt((k * k).sum(-1, keepdims=True) + 1e-6)
-    beta = 1.0 / (1.0 + np.exp(-(h @ w[p + "b"].T)))
-    decay = np.exp(-np.exp(w[p + "A_log"]) * softplus(h @ w[p + "a"].T + w[p + "dt_bias"]))
+    beta = 1.0 / (1.0 + np.exp(-linear(h, w[p + "b"])))
+    decay = np.exp(-np.exp(w[p + "A_log"]) * softplus(linear(h, w[p + "a"]) + w[p + "dt_bias"]))
     o = np.zeros((T, H, dv))
     for i in range(H):
         g = i // (H // G)
         o[:, i] = delta_rule(q[:, g], k[:, g], v[:, i], beta[:, i], decay[:, i])
-    o = rms_unit(o, eps) * w[p + "norm"] * silu(h @ w[p + "g"].T).reshape(T, H, dv)
-    return o.reshape(T, -1) @ w[p + "o"].T
+    o = rms_unit(o, eps) * w[p + "norm"] * silu(linear(h, w[p + "g"])).reshape(T, H, dv)
+    return linear(o.reshape(T, -1), w[p + "o"])
 
 
 def parallel_mixer(h, w, p, m, eps):
@@ -181,17 +210,27 @@ def parallel_mixer(h, w, p, m, eps):
 # ---- feed-forward ---------------------------------------------------------------------------------
 
 
+def choose_experts(z, top):
+    """z [T, n] router logits -> (indices [T, top], weights [T, top]): the `top` largest logits of every row
+    (the lower index wins a tie), weighted by the softmax over those logits alone."""
+    idx = np.stack([np.array(sorted(range(z.shape[1]), key=lambda e: (-row[e], e))[:top]) for row in z])
+    chosen = np.take_along_axis(z, idx, axis=1)
+    e_w = np.exp(chosen - chosen.max(axis=1, keepdims=True))
+    return idx, e_w / e_w.sum(axis=1, keepdims=True)
+
+
+def gated_expert(h, gate, up, down):
+    return linear(kept(silu(linear(h, gate, True)) * linear(h, up, True)), down, True)
+
+
 def routed_ff(h, w, p, mlp):
     n, top = mlp["router"]["experts"], mlp["router"]["top"]
-    z = h @ w[p + "router"].T + w[p + "router.b"]
+    idx, wts = choose_experts(linear(h, w[p + "router"], exact_result=True) + w[p + "router.b"], top)
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
-        chosen = sorted(range(n), key=lambda e: (-z[t, e], e))[:top]
-        e_w = np.exp(z[t, chosen] - z[t, chosen].max())
-        e_w /= e_w.sum()
-        for e, g in zip(chosen, e_w):
+        for e, g in zip(idx[t], wts[t]):
             q = f"{p}e{e}."
-            out[t] += g * ((silu(h[t] @ w[q + "gate"].T) * (h[t] @ w[q + "up"].T)) @ w[q + "down"].T)
+            out[t] += g * gated_expert(h[t], w[q + "gate"], w[q + "up"], w[q + "down"])
     return out
 
 
@@ -211,5 +250,5 @@ def forward(cfg: dict, w: dict, tokens):
         if layer.get("mlp") is not None:
             x = rms_unit(alpha * x + routed_ff(x, w, p + "mlp.", layer["mlp"]), eps) * w[p + "norm2"]
         streams.append(x)
-    logits = (rms_unit(x, eps) * w["final.norm"]) @ w["head"].T
+    logits = linear(rms_unit(x, eps) * w["final.norm"], w["head"], exact_result=True)
     return logits, np.stack(streams)
