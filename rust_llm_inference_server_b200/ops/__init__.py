@@ -346,7 +346,10 @@ def gated_delta(proj: torch.Tensor, qkv_off: int, b_off: int, a_off: int, conv_w
     logit a head of beta from b_off and of the decay from a_off), a causal convolution of `taps` taps per channel
     (conv_w float32 [C, taps]) and silu, unit vectors q (times q_scale) and k, then per head S <- g S, u = beta
     (v - S^T k), S <- S + k u^T, o = S^T q.  `state` float32 [slots, gated_delta_state_floats(...)] holds S and
-    the convolution's tail between steps; out float32 [T, nh dv]."""
+    the convolution's tail between steps; out float32 [T, nh dv].
+
+    A step with more than four tokens a request on average (one with prompts) goes through the kernel that takes
+    16 tokens of a request at a time; steps of single tokens and short portions walk token by token."""
     T, N = proj.shape
     C = 2 * n_qk_heads * d + n_heads * dv
     _req(proj, "proj")
@@ -358,14 +361,19 @@ def gated_delta(proj: torch.Tensor, qkv_off: int, b_off: int, a_off: int, conv_w
     if qkv_off + C > N or b_off + n_heads > N or a_off + n_heads > N:
         raise KernelError("gated_delta: the column offsets reach beyond the projection's rows")
     act = step.buffer("gated_delta_act", (T, C + 2 * n_heads), torch.float32)
+    chunks = T > 4 * step.n_seqs
+    gram = step.buffer("gated_delta_gram", (T, n_qk_heads * 32 + n_heads * 16), torch.float32).data_ptr() if chunks else 0
     check(lib().rlis_gated_delta(proj.data_ptr(), proj.stride(0), int(qkv_off), int(b_off), int(a_off), conv_w.data_ptr(),
                                  a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), state.stride(0),
                                  step.cu_seqlens.data_ptr(), step.ctx_lens.data_ptr(), step.state_slots.data_ptr(),
-                                 step.seq_of_token.data_ptr(), act.data_ptr(), out.data_ptr(), T, step.n_seqs, n_heads,
+                                 step.seq_of_token.data_ptr(), act.data_ptr(), gram, out.data_ptr(), T, step.n_seqs, n_heads,
                                  n_qk_heads, d, dv, taps, float(unit_eps), float(q_scale), _code(proj.dtype), _stream()),
           "gated_delta")
     _count("gated_delta.prepare")
-    _count("gated_delta.scan")
+    if chunks:
+        _count("gated_delta.gram")
+        _count("gated_delta.solve")
+    _count("gated_delta.chunks" if chunks else "gated_delta.scan")
     return out
 
 

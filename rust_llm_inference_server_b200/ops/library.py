@@ -32,7 +32,7 @@ SIGNATURES = {
     "rlis_post_norm_residual": [P, P, P, P, P, P, P, I, I, F, F, F, I, P],
     "rlis_sum_norm": [P, P, F, P, P, F, P, F, P, P, I, I, F, F, I, P],
     "rlis_head_norm_gate": [P, P, P, LL, P, I, I, I, F, I, I, P],
-    "rlis_gated_delta": [P, LL, I, I, I, P, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, I, P],
+    "rlis_gated_delta": [P, LL, I, I, I, P, P, P, P, LL, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, I, P],
     "rlis_gated_delta_state_floats": [I, I, I, I, I],
     "rlis_act_norm": [P, LL, I, P, P, LL, P, LL, I, I, F, I, P],
     "rlis_bias_act": [P, P, P, LL, I, I, I, P],
