@@ -20,9 +20,9 @@
 // scan:    (steps of single tokens and short portions) columns of S evolve independently: a CTA takes (request,
 //          head, 16 columns), 16 threads share a column (each a contiguous share of its entries in registers) and
 //          walk the request's tokens of this step in order; the column's dot product with k is summed over the 16
-//          threads by shuffles, the read-out's partial sums after each tile of tokens.  The CTA of head 0, columns
-//          0 also moves the slot's convolution tail on (after every reader of the old one is done: the prepare
-//          kernel has finished).
+//          threads by shuffles, the read-out's partial sums after each tile of tokens.  The request's CTAs also
+//          move the slot's convolution tail on, a share of the channels each (every reader of the old one is
+//          done: the prepare kernel has finished).
 // chunks:  (steps with prompts) the same CTAs and threads take 16 tokens at a time.  With L_t the sum of ln g
 //          over the chunk's tokens up to t and S0 the state before the chunk,
 //              u_t = beta_t (v_t - e^{L_t} S0^T k_t) - sum_{i<t} beta_t e^{L_t - L_i} (k_t . k_i) u_i
@@ -96,19 +96,11 @@ __global__ __launch_bounds__(PREP_WARPS * 32) void delta_prepare_kernel(
     const int c0 = unit_norm ? u * d : 2 * n_qk * d + (u - 2 * n_qk) * dv;
     const T* x = proj + qkv_off;
     float ss = 0.f;
-#pragma unroll 2
     for (int j = lane; j < width; j += 32) {
         const int c = c0 + j;
-        float in[MAX_TAPS], w[MAX_TAPS];           // all loads first, then the sum in the order of the taps
-#pragma unroll
-        for (int k = 0; k < MAX_TAPS; ++k) {
-            in[k] = k < taps ? conv_input<T>(x, stride, row0, li - (taps - 1 - k), c, C, tail, taps, fresh) : 0.f;
-            w[k] = k < taps ? conv_w[(size_t)c * taps + k] : 0.f;
-        }
         float acc = 0.f;
-#pragma unroll
-        for (int k = 0; k < MAX_TAPS; ++k)
-            if (k < taps) acc = fmaf(w[k], in[k], acc);
+        for (int k = 0; k < taps; ++k)
+            acc = fmaf(conv_w[(size_t)c * taps + k], conv_input<T>(x, stride, row0, li - (taps - 1 - k), c, C, tail, taps, fresh), acc);
         const float y = silu_f(acc);
         ss = fmaf(y, y, ss);
         arow[c] = y;
@@ -147,11 +139,12 @@ __global__ __launch_bounds__(THREADS) void delta_scan_kernel(
     float* slot = state + (size_t)sq.state_slots[b] * state_stride;
     const int C = 2 * n_qk * d + nh * dv;
     const int AW = C + 2 * nh;
-    if (h == 0 && blockIdx.z == 0 && taps > 1) {
-        // the tail of the convolution after this step: the last taps - 1 inputs of the request
+    if (taps > 1) {
+        // the tail of the convolution after this step: the last taps - 1 inputs of the request, the channels
+        // shared out among the request's CTAs (a channel's old tail is read by the thread that replaces it)
         float* tail = slot + tail_off;
         const T* x = proj + qkv_off;
-        for (int c = threadIdx.x; c < C; c += THREADS) {
+        for (int c = (h * gridDim.z + blockIdx.z) * THREADS + threadIdx.x; c < C; c += nh * gridDim.z * THREADS) {
             float nv[MAX_TAPS - 1];
 #pragma unroll
             for (int j = 0; j < MAX_TAPS - 1; ++j)
@@ -339,15 +332,17 @@ __global__ __launch_bounds__(GRAM_WARPS * 32) void delta_solve_kernel(
         const float up = __shfl_up_sync(0xffffffffu, L, o, CH);
         if (j >= o) L += up;
     }
-    float col[CH];                                  // col[a] = W[a][j]
+    float col[CH], kk[CH];                          // col[a] = W[a][j];  kk[a] = k_a . k_j
+#pragma unroll
+    for (int a = 0; a < CH; ++a)
+        kk[a] = j < a && a <= back ? gram[(size_t)(r0 + a) * GW + hq * 2 * CH + (a - j)] : 0.f;
 #pragma unroll
     for (int a = 0; a < CH; ++a) {
         col[a] = 0.f;
         if (a <= back) {                            // the same for the whole warp
             // lane i < a: M[a][i]
             const float La = __shfl_sync(0xffffffffu, L, a), ba = __shfl_sync(0xffffffffu, beta, a);
-            const float g = j < a ? gram[(size_t)(r0 + a) * GW + hq * 2 * CH + (a - j)] : 0.f;
-            const float mi = j < a ? ba * expf(La - L) * g : 0.f;
+            const float mi = j < a ? ba * expf(La - L) * kk[a] : 0.f;
             float acc = j == a ? 1.f : 0.f;
 #pragma unroll
             for (int i = 0; i < a; ++i) acc = fmaf(-__shfl_sync(0xffffffffu, mi, i), col[i], acc);
@@ -414,11 +409,12 @@ __global__ __launch_bounds__(CTHREADS) void delta_chunk_kernel(
     float* slot = state + (size_t)sq.state_slots[b] * state_stride;
     const int C = 2 * n_qk * d + nh * dv;
     const int AW = C + 2 * nh, GW = n_qk * 2 * CH + nh * CH;
-    if (h == 0 && blockIdx.z == 0 && taps > 1) {
-        // the tail of the convolution after this step: the last taps - 1 inputs of the request
+    if (taps > 1) {
+        // the tail of the convolution after this step: the last taps - 1 inputs of the request, the channels
+        // shared out among the request's CTAs (a channel's old tail is read by the thread that replaces it)
         float* tail = slot + tail_off;
         const T* x = proj + qkv_off;
-        for (int c = threadIdx.x; c < C; c += CTHREADS) {
+        for (int c = (h * gridDim.z + blockIdx.z) * CTHREADS + threadIdx.x; c < C; c += nh * gridDim.z * CTHREADS) {
             float nv[MAX_TAPS - 1];
 #pragma unroll
             for (int j = 0; j < MAX_TAPS - 1; ++j)
@@ -692,8 +688,13 @@ extern "C" int rlis_gated_delta(const void* proj, long long stride, int qkv_off,
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     }
     const bool spread = (long long)grid.x * grid.y * grid.z <= sms;
-#define RLIS_DELTA(T, E) rlis_launch(delta_scan_kernel<T, E>, grid, THREADS, 0, stream, act, out, state, state_stride, \
-                                     tail_off, (const T*)proj, stride, qkv_off, sq, nh, n_qk, d, dv, taps)
+#define RLIS_DELTA(T, E)                                                                                                 \
+    do {                                                                                                                 \
+        const size_t bytes = spread && n_tokens > n_seqs ? 120 * 1024 : 0;                                               \
+        if (bytes) cudaFuncSetAttribute(delta_scan_kernel<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes); \
+        rlis_launch(delta_scan_kernel<T, E>, grid, THREADS, bytes, stream, act, out, state, state_stride, tail_off,      \
+                    (const T*)proj, stride, qkv_off, sq, nh, n_qk, d, dv, taps);                                         \
+    } while (0)
 #define RLIS_CHUNK(T, E)                                                                                                 \
     do {                                                                                                                 \
         size_t bytes = chunk_smem_floats(E) * sizeof(float);                                                             \

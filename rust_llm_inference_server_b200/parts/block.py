@@ -209,11 +209,9 @@ class PostNormBlock:
         h = pending.x if isinstance(pending, StreamRows) else self._stream(resid, step)
         chained = isinstance(next_block, (PostNormBlock, OutNormBlock)) and next_block.dtype == self.dtype
         branches = getattr(self.mixer, "forward_branches", None)
-        if branches is not None:
+        if branches is not None and len(self.mixer.branches) <= 2:      # the joining kernel takes two terms
             terms, eps_b = branches(h, step, cache, state, writes_cache)
         else:
-            terms, eps_b = [(self.mixer.forward(h, step, cache, state, writes_cache), None, 1.0)], 0.0
-        if len(terms) > 2:
             terms, eps_b = [(self.mixer.forward(h, step, cache, state, writes_cache), None, 1.0)], 0.0
         h = self._join(terms, eps_b, self.norm1, resid, step, chained or self.feed_forward is not None)
         if self.feed_forward is not None:

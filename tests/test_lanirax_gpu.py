@@ -322,7 +322,8 @@ def test_recurrence_cut_into_portions_over_slots_that_held_something_else(dtype,
         st.state_slots = dev([slot_of[r] for r, _ in entries], torch.int32)
         proj = dev(np.concatenate([rows[r][done[r]:done[r] + n] for r, n in entries]), dtype)
         out = torch.full((st.n_tokens, nh * dv), float("nan"), dtype=torch.float32, device="cuda")
-        ops.gated_delta(proj, q_off, b_off, a_off, taps_w, a_log, dt_bias, state, out, st, nh, nqk, d, dv, taps, 1e-6, d ** -0.5)
+        ops.gated_delta(proj, q_off, b_off, a_off, taps_w, a_log, dt_bias, state, out, st, nh, nqk, d, dv, taps, 1e-6, d ** -0.5,
+                        chunks=st.n_tokens > 4 * st.n_seqs)
         got, at = host(out).reshape(-1, nh, dv), 0
         for r, n in entries:
             worst = max(worst, float(np.abs(got[at:at + n] - want[r][done[r]:done[r] + n]).max()))
@@ -421,9 +422,12 @@ def test_the_stream_after_every_run_of_a_layer(model_root, which):
                                              ("B", 16, [3, 150, 40, 2, 129, 1]), ("B", 32, [260, 31, 5, 90]),
                                              ("C", 16, [1, 70, 333, 2, 129, 64, 65]), ("C", 8, [200, 31, 5, 400]),
                                              ("D", 16, [90, 1, 33, 150, 2]), ("E", 16, [420, 3, 200, 77])])
-def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, lens, dtype):
+def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, lens, dtype, monkeypatch):
     from rust_llm_inference_server_b200 import ops
     ops.launches_by_kernel.clear()
+    # portions of five tokens and more go through the recurrence's chunk kernels, shorter ones token by token: every
+    # family of cuts mixes the two
+    monkeypatch.setattr(ops, "GATED_DELTA_CHUNKS_FROM", 5)
     d = model_dir(model_root, which, dtype)
     reqs = requests_for(U.CONFIGS[which], lens, seed=page)
     ref = plain_logits(d, reqs, dtype)
