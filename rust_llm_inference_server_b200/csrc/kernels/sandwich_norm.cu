@@ -113,7 +113,8 @@ __global__ __launch_bounds__(THREADS) void act_norm_kernel(
     }
 }
 
-template <typename T>
+// PT = entries of a row that a thread keeps (the width over 256, rounded up to 4, 8 or 32).
+template <typename T, int PT>
 __global__ __launch_bounds__(THREADS) void sum_norm_kernel(
     const T* __restrict__ a, const float* __restrict__ wa, float ca, const T* __restrict__ b,
     const float* __restrict__ wb, float cb, float* __restrict__ resid, float alpha, const float* __restrict__ w_out,
@@ -121,10 +122,10 @@ __global__ __launch_bounds__(THREADS) void sum_norm_kernel(
     pdl_wait_and_trigger();
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * hidden;
-    float va[MAX_PER_THREAD], vb[MAX_PER_THREAD];
+    float va[PT], vb[PT];
     float sa = 0.f, sb = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_PER_THREAD; ++i) {
+    for (int i = 0; i < PT; ++i) {
         const int c = threadIdx.x + i * THREADS;
         va[i] = vb[i] = 0.f;
         if (c < hidden) {
@@ -139,7 +140,7 @@ __global__ __launch_bounds__(THREADS) void sum_norm_kernel(
     if (b != nullptr && wb != nullptr) rb = cb / sqrtf(block_sum(sb, scratch) / (float)hidden + eps_branch);
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_PER_THREAD; ++i) {
+    for (int i = 0; i < PT; ++i) {
         const int c = threadIdx.x + i * THREADS;
         if (c < hidden) {
             float y = resid != nullptr ? alpha * resid[base + c] : 0.f;
@@ -152,7 +153,7 @@ __global__ __launch_bounds__(THREADS) void sum_norm_kernel(
     float r = 1.0f;
     if (w_out != nullptr) r = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps_out);
 #pragma unroll
-    for (int i = 0; i < MAX_PER_THREAD; ++i) {
+    for (int i = 0; i < PT; ++i) {
         const int c = threadIdx.x + i * THREADS;
         if (c < hidden) {
             const float y = w_out != nullptr ? va[i] * r * w_out[c] : va[i];
@@ -455,14 +456,20 @@ extern "C" int rlis_sum_norm(const void* a, const float* wa, float ca, const voi
                              float eps_branch, float eps_out, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || hidden > THREADS * MAX_PER_THREAD || (resid == nullptr && out == nullptr)) return RLIS_ERR_UNSUPPORTED;
-    if (dtype == RLIS_F32)
-        rlis_launch(sum_norm_kernel<float>, n_tokens, THREADS, 0, stream, (const float*)a, wa, ca, (const float*)b, wb, cb,
-                    resid, alpha, w_out, (float*)out, hidden, eps_branch, eps_out);
-    else if (dtype == RLIS_BF16)
-        rlis_launch(sum_norm_kernel<bf16>, n_tokens, THREADS, 0, stream, (const bf16*)a, wa, ca, (const bf16*)b, wb, cb,
-                    resid, alpha, w_out, (bf16*)out, hidden, eps_branch, eps_out);
-    else
-        return RLIS_ERR_UNSUPPORTED;
+#define RLIS_SUM_NORM(T, PT)                                                                                       \
+    rlis_launch(sum_norm_kernel<T, PT>, n_tokens, THREADS, 0, stream, (const T*)a, wa, ca, (const T*)b, wb, cb, resid, \
+                alpha, w_out, (T*)out, hidden, eps_branch, eps_out)
+#define RLIS_SUM_NORM_T(T)                                                                                         \
+    do {                                                                                                           \
+        if (hidden <= THREADS * 4) RLIS_SUM_NORM(T, 4);                                                            \
+        else if (hidden <= THREADS * 8) RLIS_SUM_NORM(T, 8);                                                       \
+        else RLIS_SUM_NORM(T, MAX_PER_THREAD);                                                                     \
+    } while (0)
+    if (dtype == RLIS_F32) RLIS_SUM_NORM_T(float);
+    else if (dtype == RLIS_BF16) RLIS_SUM_NORM_T(bf16);
+    else return RLIS_ERR_UNSUPPORTED;
+#undef RLIS_SUM_NORM_T
+#undef RLIS_SUM_NORM
     return RLIS_LAUNCH_CHECK();
 }
 
