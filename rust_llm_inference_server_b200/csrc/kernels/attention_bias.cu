@@ -12,6 +12,10 @@
 // (cos and sin times `rot_mag`); queries are multiplied, after their norm, by 1 + coef * ln(floor((p + 1) /
 // every) + 1) at position p; slope_h * (i - j) is subtracted from a score; exp(sink_h) joins the softmax's
 // denominator (a term without key or value).  Values that are the keys as projected are had by v_off = k_off.
+// `rot_half`: the rotation pairs entry i with entry i + rot_dims / 2 instead (the pair (a, b) becomes (a cos - b sin,
+// b cos + a sin) either way).  `proj_bias` (float32, one entry a column of the projection's row): added to queries,
+// keys and values as they are read.  `gate_cols` > 1: the gate has one logit a channel of every head (gate[t, h *
+// dv + c]) instead of one a head.
 //
 // `bias` is a float32 table [n_dist, n_heads] by distance (the host turns bucket rules into it; all
 // distances from n_dist - 1 on share the last row).  Norms, scores, softmax, value sums, the mixing and
@@ -37,7 +41,7 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_kernel(
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots,
     int n_units, int nh, int nkv, int d, int dv, int page_size,
     const float* __restrict__ inv_freq, int rot_dims, float rot_mag, const int* __restrict__ positions,
-    float q_temp_coef, int q_temp_every) {
+    float q_temp_coef, int q_temp_every, int rot_half, const float* __restrict__ proj_bias) {
     pdl_wait_and_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int unit = blockIdx.x * WARPS + warp;
@@ -46,17 +50,35 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_kernel(
     const int t = unit / per, u = unit - t * per;
     const T* row = proj + (size_t)t * stride;
     const bool is_q = u < nh;
-    const T* x = row + (is_q ? q_off + u * d : k_off + (u - nh) * d);
+    const int x_col = is_q ? q_off + u * d : k_off + (u - nh) * d;
+    const T* x = row + x_col;
+    const float* xb = proj_bias != nullptr ? proj_bias + x_col : nullptr;
     const float* w = is_q ? q_w : k_w;
     float v[MAX_D / 32];
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) {
         const int c = lane + 32 * i;
-        v[i] = c < d ? to_f<T>(x[c]) : 0.f;
+        v[i] = c < d ? to_f<T>(x[c]) + (xb != nullptr ? xb[c] : 0.f) : 0.f;
     }
     const int pos = positions != nullptr ? positions[t] : 0;
-    if (rot_dims > 0) {
+    if (rot_dims > 0 && rot_half) {
+        // entry c turns with entry c +- rot_dims / 2, read again from the row
+        const int half = rot_dims >> 1;
+#pragma unroll
+        for (int i = 0; i < MAX_D / 32; ++i) {
+            const int c = lane + 32 * i;
+            if (c < rot_dims) {
+                const int pc = c < half ? c + half : c - half;
+                const float other = to_f<T>(x[pc]) + (xb != nullptr ? xb[pc] : 0.f);
+                float sn, cs;
+                sincosf((float)pos * inv_freq[c < half ? c : pc], &sn, &cs);
+                sn *= rot_mag;
+                cs *= rot_mag;
+                v[i] = c < half ? rope_first(v[i], other, cs, sn) : rope_second(other, v[i], cs, sn);
+            }
+        }
+    } else if (rot_dims > 0) {
         // lanes 2j and 2j+1 hold a pair (32 i is even)
 #pragma unroll
         for (int i = 0; i < MAX_D / 32; ++i) {
@@ -101,9 +123,10 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_kernel(
     if (vrow >= 0) {
         const int g = u - nh;
         const T* vs = row + v_off + g * dv;
+        const float* vb = proj_bias != nullptr ? proj_bias + v_off + g * dv : nullptr;
         const T* vo = v_other != nullptr ? v_other + (size_t)t * v_other_stride + g * dv : nullptr;
         for (int c = lane; c < dv; c += 32) {
-            float val = to_f<T>(vs[c]);
+            float val = to_f<T>(vs[c]) + (vb != nullptr ? vb[c] : 0.f);
             if (vo != nullptr) val = (1.0f - lambda) * val + lambda * to_f<T>(vo[c]);
             v_cache[vrow + c] = from_f<T>(val);
         }
@@ -121,7 +144,7 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_vec_kernel(
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots,
     int n_units, int nh, int nkv, int d, int dv, int page_size, int lanes,
     const float* __restrict__ inv_freq, int rot_dims, float rot_mag, const int* __restrict__ positions,
-    float q_temp_coef, int q_temp_every) {
+    float q_temp_coef, int q_temp_every, int rot_half, const float* __restrict__ proj_bias) {
     pdl_wait_and_trigger();
     constexpr int VN = Vec16<T>::N;
     const int lane = threadIdx.x & 31;
@@ -133,12 +156,36 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_vec_kernel(
     const int t = live ? unit / per : 0, u = live ? unit - t * per : 0;
     const T* row = proj + (size_t)t * stride;
     const bool is_q = u < nh;
-    const T* x = row + (is_q ? q_off + u * d : k_off + (u - nh) * d);
+    const int x_col = is_q ? q_off + u * d : k_off + (u - nh) * d;
+    const T* x = row + x_col;
+    const float* xb = proj_bias != nullptr ? proj_bias + x_col : nullptr;
     const float* w = is_q ? q_w : k_w;
     float v[VN];
     load16<T>(x + li * VN, v);
+    if (xb != nullptr) {
+#pragma unroll
+        for (int i = 0; i < VN; ++i) v[i] += xb[li * VN + i];
+    }
     const int pos = positions != nullptr ? positions[t] : 0;
-    if (rot_dims > 0) {
+    if (rot_dims > 0 && rot_half) {
+        // a lane's VN entries lie in one half of the rotated part (rot_dims / 2 is a multiple of VN): their
+        // partners are the VN entries rot_dims / 2 further on or back, read again from the row
+        const int half = rot_dims >> 1, c0 = li * VN;
+        if (c0 < rot_dims) {
+            const int p0 = c0 < half ? c0 + half : c0 - half;
+            float o[VN];
+            load16<T>(x + p0, o);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) {
+                if (xb != nullptr) o[i] += xb[p0 + i];
+                float sn, cs;
+                sincosf((float)pos * inv_freq[(c0 < half ? c0 : p0) + i], &sn, &cs);
+                sn *= rot_mag;
+                cs *= rot_mag;
+                v[i] = c0 < half ? rope_first(v[i], o[i], cs, sn) : rope_second(o[i], v[i], cs, sn);
+            }
+        }
+    } else if (rot_dims > 0) {
         // a lane's VN entries are whole pairs
 #pragma unroll
         for (int i = 0; i < VN; i += 2) {
@@ -187,6 +234,10 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_vec_kernel(
         for (int c = li * VN; c < dv; c += lanes * VN) {
             float a[VN];
             load16<T>(vs + c, a);
+            if (proj_bias != nullptr) {
+#pragma unroll
+                for (int i = 0; i < VN; ++i) a[i] += proj_bias[v_off + g * dv + c + i];
+            }
             if (vo != nullptr) {
                 float b[VN];
                 load16<T>(vo + c, b);
@@ -207,7 +258,7 @@ __global__ __launch_bounds__(WARPS * 32) void attn_bias_kernel(
     const float* __restrict__ bias, int n_dist, const T* __restrict__ gate, long long gate_stride,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, const int* __restrict__ block_tables,
     const int* __restrict__ token_rows, int max_blocks, int n_rows, int nh, int nkv, int d, int dv, int page_size,
-    float scale, int window, const float* __restrict__ sinks, const float* __restrict__ slopes) {
+    float scale, int window, const float* __restrict__ sinks, const float* __restrict__ slopes, int gate_cols) {
     pdl_wait();
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -282,13 +333,19 @@ __global__ __launch_bounds__(WARPS * 32) void attn_bias_kernel(
         for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= corr;
     }
     float g = 1.0f;
-    if (gate != nullptr) g = 1.0f / (1.0f + expf(-to_f<T>(gate[(size_t)t * gate_stride + h])));
+    const bool by_channel = gate != nullptr && gate_cols > 1;
+    if (gate != nullptr && !by_channel) g = 1.0f / (1.0f + expf(-to_f<T>(gate[(size_t)t * gate_stride + h])));
     T* orow = out + ((size_t)t * nh + h) * dv;
     const float inv_l = g / l;
+    const T* grow = by_channel ? gate + (size_t)t * gate_stride + (size_t)h * dv : nullptr;
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) {
         const int c = lane + 32 * i;
-        if (c < dv) orow[c] = from_f<T>(acc[i] * inv_l);
+        if (c < dv) {
+            float y = acc[i] * inv_l;
+            if (by_channel) y *= 1.0f / (1.0f + expf(-to_f<T>(grow[c])));
+            orow[c] = from_f<T>(y);
+        }
     }
     pdl_trigger();
 }
@@ -303,7 +360,8 @@ extern "C" int rlis_qk_norm_store(const void* proj, long long stride, int q_off,
                                   long long v_other_stride, float lambda, void* q_out, void* k_cache, void* v_cache,
                                   const int* slots, int n_tokens, int nh, int nkv, int d, int dv, int page_size,
                                   const float* inv_freq, int rot_dims, float rot_mag, const int* positions,
-                                  float q_temp_coef, int q_temp_every, int dtype, cudaStream_t stream) {
+                                  float q_temp_coef, int q_temp_every, int rot_half, const float* proj_bias, int dtype,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0 || d > MAX_D || dv <= 0 || nh <= 0 || nkv <= 0) return RLIS_ERR_UNSUPPORTED;
     if (rot_dims < 0 || rot_dims > d || (rot_dims & 1) || (rot_dims > 0 && (inv_freq == nullptr || positions == nullptr)) ||
@@ -320,7 +378,8 @@ extern "C" int rlis_qk_norm_store(const void* proj, long long stride, int q_off,
                                reinterpret_cast<uintptr_t>(v_cache);
         const bool vec = (dtype == RLIS_F32 || dtype == RLIS_BF16) && d % vn == 0 && dv % vn == 0 && lanes >= 1 &&
                          lanes <= 32 && (lanes & (lanes - 1)) == 0 && (ptrs & 15) == 0 && stride % vn == 0 &&
-                         v_other_stride % vn == 0 && q_off % vn == 0 && k_off % vn == 0 && v_off % vn == 0;
+                         v_other_stride % vn == 0 && q_off % vn == 0 && k_off % vn == 0 && v_off % vn == 0 &&
+                         (!rot_half || rot_dims == 0 || (rot_dims / 2) % vn == 0);
         if (vec) {
             const int per_warp = 32 / lanes;
             const unsigned vblocks = (unsigned)((units + (long long)WARPS * per_warp - 1) / (WARPS * per_warp));
@@ -328,12 +387,12 @@ extern "C" int rlis_qk_norm_store(const void* proj, long long stride, int q_off,
                 rlis_launch(qk_norm_store_vec_kernel<float>, vblocks, WARPS * 32, 0, stream, (const float*)proj, stride, q_off,
                             k_off, v_off, q_w, k_w, eps, (const float*)v_other, v_other_stride, lambda, (float*)q_out,
                             (float*)k_cache, (float*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, lanes, inv_freq, rot_dims,
-                            rot_mag, positions, q_temp_coef, q_temp_every);
+                            rot_mag, positions, q_temp_coef, q_temp_every, rot_half, proj_bias);
             else
                 rlis_launch(qk_norm_store_vec_kernel<bf16>, vblocks, WARPS * 32, 0, stream, (const bf16*)proj, stride, q_off,
                             k_off, v_off, q_w, k_w, eps, (const bf16*)v_other, v_other_stride, lambda, (bf16*)q_out,
                             (bf16*)k_cache, (bf16*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, lanes, inv_freq, rot_dims,
-                            rot_mag, positions, q_temp_coef, q_temp_every);
+                            rot_mag, positions, q_temp_coef, q_temp_every, rot_half, proj_bias);
             return RLIS_LAUNCH_CHECK();
         }
     }
@@ -342,12 +401,12 @@ extern "C" int rlis_qk_norm_store(const void* proj, long long stride, int q_off,
         rlis_launch(qk_norm_store_kernel<float>, blocks, WARPS * 32, 0, stream, (const float*)proj, stride, q_off, k_off,
                     v_off, q_w, k_w, eps, (const float*)v_other, v_other_stride, lambda, (float*)q_out, (float*)k_cache,
                     (float*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, inv_freq, rot_dims, rot_mag, positions,
-                    q_temp_coef, q_temp_every);
+                    q_temp_coef, q_temp_every, rot_half, proj_bias);
     else if (dtype == RLIS_BF16)
         rlis_launch(qk_norm_store_kernel<bf16>, blocks, WARPS * 32, 0, stream, (const bf16*)proj, stride, q_off, k_off,
                     v_off, q_w, k_w, eps, (const bf16*)v_other, v_other_stride, lambda, (bf16*)q_out, (bf16*)k_cache,
                     (bf16*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, inv_freq, rot_dims, rot_mag, positions,
-                    q_temp_coef, q_temp_every);
+                    q_temp_coef, q_temp_every, rot_half, proj_bias);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();
@@ -355,15 +414,16 @@ extern "C" int rlis_qk_norm_store(const void* proj, long long stride, int q_off,
 
 // q [T, nh d]; k_cache [pages, nkv, page_size, d]; v_cache [pages, nkv, page_size, dv]; out [T, nh dv];
 // bias float32 [n_dist, nh] or null; gate (null: none): logits, head h of token t at gate[t * gate_stride + h];
-// sinks, slopes float32 [nh] or null.
+// sinks, slopes float32 [nh] or null.  gate_cols dv: the gate has a logit a channel, gate[t * gate_stride + h * dv + c].
 extern "C" int rlis_attention_bias(const void* q, const void* k_cache, const void* v_cache, void* out,
                                    const float* bias, int n_dist, const void* gate, long long gate_stride,
                                    const int* seq_of_token, const int* positions, const int* block_tables,
                                    const int* token_rows, int max_blocks, int n_tokens, int nh, int nkv, int d, int dv,
                                    int page_size, float scale, int window, const float* sinks, const float* slopes,
-                                   int dtype, cudaStream_t stream) {
+                                   int gate_cols, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (d <= 0 || d > MAX_D || dv <= 0 || dv > MAX_D || nkv <= 0 || nh % nkv != 0 || (bias != nullptr && n_dist <= 0))
+    if (d <= 0 || d > MAX_D || dv <= 0 || dv > MAX_D || nkv <= 0 || nh % nkv != 0 || (bias != nullptr && n_dist <= 0) ||
+        (gate != nullptr && gate_cols != 1 && gate_cols != dv))
         return RLIS_ERR_UNSUPPORTED;
     const long long n_rows = (long long)n_tokens * nh;
     if (n_rows > 0x7fffffffLL) return RLIS_ERR_UNSUPPORTED;
@@ -373,12 +433,12 @@ extern "C" int rlis_attention_bias(const void* q, const void* k_cache, const voi
         rlis_launch(attn_bias_kernel<float>, blocks, WARPS * 32, smem, stream, (const float*)q, (const float*)k_cache,
                     (const float*)v_cache, (float*)out, bias, n_dist, (const float*)gate, gate_stride, seq_of_token,
                     positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, dv, page_size, scale, window,
-                    sinks, slopes);
+                    sinks, slopes, gate_cols);
     else if (dtype == RLIS_BF16)
         rlis_launch(attn_bias_kernel<bf16>, blocks, WARPS * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache,
                     (const bf16*)v_cache, (bf16*)out, bias, n_dist, (const bf16*)gate, gate_stride, seq_of_token,
                     positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, dv, page_size, scale, window,
-                    sinks, slopes);
+                    sinks, slopes, gate_cols);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

@@ -85,7 +85,8 @@ __global__ __launch_bounds__(THREADS, (D + DV <= 128) ? 4 : 3) void attn_bias_pr
     bf16* __restrict__ out, const float* __restrict__ bias, int n_dist, const bf16* __restrict__ gate,
     long long gate_stride, const int* __restrict__ tiles, const int* __restrict__ cu_seqlens,
     const int* __restrict__ ctx_lens, const int* __restrict__ block_tables, int max_blocks, int nh, int nkv,
-    int page_size, float scale, int window, const float* __restrict__ sinks, const float* __restrict__ slopes) {
+    int page_size, float scale, int window, const float* __restrict__ sinks, const float* __restrict__ slopes,
+    int gate_cols) {
     pdl_wait();
     constexpr int SK = D + 8, SV = DV + 8;
     constexpr int KS = D / 16, ND = DV / 8;
@@ -279,21 +280,36 @@ __global__ __launch_bounds__(THREADS, (D + DV <= 128) ? 4 : 3) void attn_bias_pr
     }
     float inv0 = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f;
     float inv1 = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
-    if (gate != nullptr) {
+    const bool by_channel = gate != nullptr && gate_cols > 1;      // a logit a channel: gate[t, head * DV + col]
+    if (gate != nullptr && !by_channel) {
         if (rv0) inv0 *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)(q_start + ti0) * gate_stride + head])));
         if (rv1) inv1 *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)(q_start + ti1) * gate_stride + head])));
     }
     if (rv0) {
         bf16* o = out + ((size_t)(q_start + ti0) * nh + head) * DV;
+        const bf16* gr = by_channel ? gate + (size_t)(q_start + ti0) * gate_stride + (size_t)head * DV : nullptr;
 #pragma unroll
-        for (int nd = 0; nd < ND; ++nd)
-            *reinterpret_cast<uint32_t*>(o + nd * 8 + 2 * c) = pack_bf16(oacc[nd][0] * inv0, oacc[nd][1] * inv0);
+        for (int nd = 0; nd < ND; ++nd) {
+            float g0 = 1.0f, g1 = 1.0f;
+            if (by_channel) {
+                g0 = 1.0f / (1.0f + expf(-__bfloat162float(gr[nd * 8 + 2 * c])));
+                g1 = 1.0f / (1.0f + expf(-__bfloat162float(gr[nd * 8 + 2 * c + 1])));
+            }
+            *reinterpret_cast<uint32_t*>(o + nd * 8 + 2 * c) = pack_bf16(oacc[nd][0] * inv0 * g0, oacc[nd][1] * inv0 * g1);
+        }
     }
     if (rv1) {
         bf16* o = out + ((size_t)(q_start + ti1) * nh + head) * DV;
+        const bf16* gr = by_channel ? gate + (size_t)(q_start + ti1) * gate_stride + (size_t)head * DV : nullptr;
 #pragma unroll
-        for (int nd = 0; nd < ND; ++nd)
-            *reinterpret_cast<uint32_t*>(o + nd * 8 + 2 * c) = pack_bf16(oacc[nd][2] * inv1, oacc[nd][3] * inv1);
+        for (int nd = 0; nd < ND; ++nd) {
+            float g0 = 1.0f, g1 = 1.0f;
+            if (by_channel) {
+                g0 = 1.0f / (1.0f + expf(-__bfloat162float(gr[nd * 8 + 2 * c])));
+                g1 = 1.0f / (1.0f + expf(-__bfloat162float(gr[nd * 8 + 2 * c + 1])));
+            }
+            *reinterpret_cast<uint32_t*>(o + nd * 8 + 2 * c) = pack_bf16(oacc[nd][2] * inv1 * g0, oacc[nd][3] * inv1 * g1);
+        }
     }
     pdl_trigger();
 }
@@ -306,7 +322,7 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
     const bf16* __restrict__ gate, long long gate_stride, const int* __restrict__ dec_rows,
     const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens, const int* __restrict__ block_tables,
     int max_blocks, int nh, int nkv, int page_size, float scale, int window, int pieces,
-    const float* __restrict__ sinks, const float* __restrict__ slopes) {
+    const float* __restrict__ sinks, const float* __restrict__ slopes, int gate_cols) {
     pdl_wait();
     constexpr int SK = D + 8, SV = DV + 8;
     constexpr int KS = D / 16, ND = DV / 8;
@@ -503,7 +519,8 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
         if (pieces == 1) {
             if (sinks != nullptr) l += exp2f(sinks[head] * LOG2E - m);
             float inv = l > 0.f ? 1.0f / l : 0.f;
-            if (gate != nullptr) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * gate_stride + head])));
+            if (gate != nullptr)
+                inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * gate_stride + (gate_cols > 1 ? head * DV + col : head)])));
             out[((size_t)row * nh + head) * DV + col] = __float2bfloat16_rn(o * inv);
         } else {
             float* p = partial + (((size_t)bi * nh + head) * pieces + piece) * MW;
@@ -516,7 +533,8 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
 // Pieces of a context into one result: one warp a (token, head).
 __global__ __launch_bounds__(128) void attn_bias_decode_merge_kernel(
     const float* __restrict__ partial, bf16* __restrict__ out, const bf16* __restrict__ gate, long long gate_stride,
-    const int* __restrict__ dec_rows, int n_units, int nh, int dv, int pieces, const float* __restrict__ sinks) {
+    const int* __restrict__ dec_rows, int n_units, int nh, int dv, int pieces, const float* __restrict__ sinks,
+    int gate_cols) {
     pdl_wait_and_trigger();
     const int unit = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (unit >= n_units) return;
@@ -533,14 +551,17 @@ __global__ __launch_bounds__(128) void attn_bias_decode_merge_kernel(
     }
     if (sinks != nullptr) l += exp2f(sinks[head] * LOG2E - m);
     float inv = l > 0.f ? 1.0f / l : 0.f;
-    if (gate != nullptr) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * gate_stride + head])));
+    const bool by_channel = gate != nullptr && gate_cols > 1;
+    if (gate != nullptr && !by_channel) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * gate_stride + head])));
     for (int col = lane; col < dv; col += 32) {
         float o = 0.f;
         for (int s = 0; s < pieces; ++s) {
             const float ms = p[(size_t)s * mw + dv];
             o = fmaf(p[(size_t)s * mw + col], ms == -INFINITY ? 0.f : exp2f(ms - m), o);
         }
-        out[((size_t)row * nh + head) * dv + col] = __float2bfloat16_rn(o * inv);
+        float gc = 1.0f;
+        if (by_channel) gc = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * gate_stride + (size_t)head * dv + col])));
+        out[((size_t)row * nh + head) * dv + col] = __float2bfloat16_rn(o * inv * gc);
     }
 }
 
@@ -573,16 +594,17 @@ extern "C" int rlis_attention_bias_prefill(const void* q, const void* k_cache, c
                                            const int* tiles, int n_tiles, const int* cu_seqlens, const int* ctx_lens,
                                            const int* block_tables, int max_blocks, int nh, int nkv, int d, int dv,
                                            int page_size, float scale, int window, const float* sinks,
-                                           const float* slopes, cudaStream_t stream) {
+                                           const float* slopes, int gate_cols, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
-    if (!sizes_taken(d, dv) || nkv <= 0 || nh % nkv != 0 || n_tiles > 65535 || (bias != nullptr && n_dist <= 0))
+    if (!sizes_taken(d, dv) || nkv <= 0 || nh % nkv != 0 || n_tiles > 65535 || (bias != nullptr && n_dist <= 0) ||
+        (gate != nullptr && gate_cols != 1 && gate_cols != dv))
         return RLIS_ERR_UNSUPPORTED;
     raise_all_once();
     dim3 grid(nh, n_tiles);
 #define RLIS_AB_PF(D_, DV_) rlis_launch(attn_bias_prefill_kernel<D_, DV_>, grid, THREADS, smem_bytes<D_, DV_>(), stream, \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, bias, n_dist, (const bf16*)gate,      \
         gate_stride, tiles, cu_seqlens, ctx_lens, block_tables, max_blocks, nh, nkv, page_size, scale, window,        \
-        sinks, slopes)
+        sinks, slopes, gate_cols)
     RLIS_AB_DISPATCH(RLIS_AB_PF)
 #undef RLIS_AB_PF
     return RLIS_LAUNCH_CHECK();
@@ -594,23 +616,25 @@ extern "C" int rlis_attention_bias_decode(const void* q, const void* k_cache, co
                                           long long gate_stride, const int* dec_rows, const int* dec_seqs,
                                           const int* ctx_lens, const int* block_tables, int max_blocks, int n_dec,
                                           int nh, int nkv, int d, int dv, int page_size, float scale, int window,
-                                          int pieces, const float* sinks, const float* slopes, cudaStream_t stream) {
+                                          int pieces, const float* sinks, const float* slopes, int gate_cols,
+                                          cudaStream_t stream) {
     if (n_dec <= 0) return 0;
     if (!sizes_taken(d, dv) || nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || pieces < 1 || pieces > 65535 ||
-        n_dec > 65535 || (bias != nullptr && n_dist <= 0) || (pieces > 1 && partial == nullptr))
+        n_dec > 65535 || (bias != nullptr && n_dist <= 0) || (pieces > 1 && partial == nullptr) ||
+        (gate != nullptr && gate_cols != 1 && gate_cols != dv))
         return RLIS_ERR_UNSUPPORTED;
     raise_all_once();
     dim3 grid(nkv, n_dec, pieces);
 #define RLIS_AB_DEC(D_, DV_) rlis_launch(attn_bias_decode_kernel<D_, DV_>, grid, THREADS, decode_smem_bytes<D_, DV_>(), stream, \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, bias, n_dist,                 \
         (const bf16*)gate, gate_stride, dec_rows, dec_seqs, ctx_lens, block_tables, max_blocks, nh, nkv, page_size,   \
-        scale, window, pieces, sinks, slopes)
+        scale, window, pieces, sinks, slopes, gate_cols)
     RLIS_AB_DISPATCH(RLIS_AB_DEC)
 #undef RLIS_AB_DEC
     int err = RLIS_LAUNCH_CHECK();
     if (err != 0 || pieces == 1) return err;
     const int units = n_dec * nh;
     rlis_launch(attn_bias_decode_merge_kernel, (units + 3) / 4, 128, 0, stream, (const float*)partial, (bf16*)out,
-                (const bf16*)gate, gate_stride, dec_rows, units, nh, dv, pieces, sinks);
+                (const bf16*)gate, gate_stride, dec_rows, units, nh, dv, pieces, sinks, gate_cols);
     return RLIS_LAUNCH_CHECK();
 }

@@ -85,6 +85,11 @@ __device__ __forceinline__ float rope_second(float a, float b, float c, float s)
     return __fmaf_rn(b, c, __fmul_rn(a, s));
 }
 
+// The gate of a gated unit: g sigmoid(slope g); slope 1 is silu, slope +inf its limit max(g, 0).
+__device__ __forceinline__ float glu_gate(float g, float slope) {
+    return slope == __int_as_float(0x7f800000) ? fmaxf(g, 0.f) : g / (1.0f + expf(-slope * g));
+}
+
 #define RLIS_LAUNCH_CHECK() ((int)cudaGetLastError())
 
 // ---- programmatic dependent launch --------------------------------------------------------

@@ -6,7 +6,7 @@
 namespace tc {
 
 // Parameters of the gated epilogue with clipping (EPI 3): g' sigmoid(slope g') (u' + shift) with g' = min(g,
-// limit) and u' = clamp(u, -limit, limit); limit +inf clips nothing.
+// limit) and u' = clamp(u, -limit, limit); limit +inf clips nothing; slope +inf: max(g', 0) (u' + shift).
 struct GluParams {
     float slope, limit, shift;
 };
@@ -42,7 +42,7 @@ __device__ __forceinline__ void store_sums32(const uint32_t (&r)[32], void* __re
                     res[tt * 4 + j] = gt / (1.0f + expf(-gt)) * up;
                 } else {
                     const float g = fminf(gt, gp.limit), u = fminf(fmaxf(up, -gp.limit), gp.limit);
-                    res[tt * 4 + j] = g / (1.0f + expf(-gp.slope * g)) * (u + gp.shift);
+                    res[tt * 4 + j] = glu_gate(g, gp.slope) * (u + gp.shift);
                 }
             }
 #pragma unroll

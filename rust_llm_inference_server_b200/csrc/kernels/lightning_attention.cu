@@ -12,6 +12,11 @@
 // memory 16 (or 8) at a time (silu applied once on the way in), the next 16 already on their way from
 // global memory while the current ones are worked on.
 // Everything after the projection is float32; the order of every sum depends on d only.
+//
+// The same walk serves recurrences whose decay differs by token and channel, S_t = diag(a_t) S_(t-1) + k_t v_t^T
+// (VEC: a is staged like k, from columns a_off of the rows), and inputs that another kernel has prepared in
+// float32 (`rlis_recurrence_inputs`: rotation of q and k by position, a scale on k, silu of q, a forget gate a = l +
+// (1 - l) sigmoid(z + b) with k = 1 - a), through `rlis_recurrence_scan`.
 #include "common.cuh"
 #include <math.h>
 
@@ -24,18 +29,20 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 // E = entries of a column that one thread holds: ceil(d / 8), rounded up to a multiple of 4 so that a
 // thread reads its share of k and q from shared memory in 16-byte vectors.  Thread `slice` owns the
 // entries slice * E .. slice * E + E - 1 (those at or beyond d stay zero).
-template <typename T, int E, bool SILU>
+template <typename T, int E, bool SILU, bool VEC>
 __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     const T* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, float* __restrict__ out,
     float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ cu_seqlens,
-    const int* __restrict__ ctx_lens, const int* __restrict__ state_slots, int nh, int d, int dv) {
+    const int* __restrict__ ctx_lens, const int* __restrict__ state_slots, int nh, int d, int dv, int a_off) {
     pdl_wait();     // (the next kernel is let in at the end: this one runs long on few warps)
-    constexpr int TOK = E > 8 ? 8 : 16;           // tokens staged at a time (shared memory holds them)
+    // tokens staged at a time (shared memory holds them; a third array with a decay a channel)
+    constexpr int TOK = VEC ? (E > 16 ? 4 : 8) : (E > 8 ? 8 : 16);
     constexpr int DP = SLICES * E;                 // padded d
     constexpr int ES = E + 4;                      // a thread's share sits 4 floats apart from the next one's: no bank conflicts
     constexpr int DPS = SLICES * ES;
     __shared__ __align__(16) float qs[TOK * DPS];
     __shared__ __align__(16) float ks[TOK * DPS];
+    __shared__ __align__(16) float as[VEC ? TOK * DPS : 4];
     __shared__ float vs[TOK * COLS];
     __shared__ __align__(16) float os[TOK * COLS * SLICES];   // a column's sixteen partial sums a token
     const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS;
@@ -45,7 +52,7 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     const bool fresh = ctx_lens[b] - n == 0;      // the request starts in this step
     const int slot = state_slots[b];
     float* S = state + (((size_t)slot * nh + h) * dv + c0 + col) * d;    // this thread's column: d contiguous entries
-    const float g = decay[h];
+    const float g = VEC ? 0.f : decay[h];
     float s[E];
     const bool quads = d % 4 == 0;                 // a thread's entries are then whole 16-byte vectors
     if (quads) {
@@ -65,7 +72,7 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     }
     // what one thread stages of q and k: element idx = threadIdx.x + j * THREADS of the [TOK][DP] tile
     constexpr int PER = TOK * DP / THREADS;
-    float rq[PER], rk[PER], rv[(TOK * COLS + THREADS - 1) / THREADS];
+    float rq[PER], rk[PER], ra[VEC ? PER : 1], rv[(TOK * COLS + THREADS - 1) / THREADS];
     auto fetch = [&](int t0) {                     // raw values of the next tokens, into registers
         const int nt = min(TOK, n - t0);
 #pragma unroll
@@ -75,6 +82,7 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
             const T* r = proj + (size_t)(row0 + t0 + (ok ? tt : 0)) * stride + h * d + (ok ? i : 0);
             rq[j] = ok ? to_f<T>(r[q_off]) : 0.f;
             rk[j] = ok ? to_f<T>(r[k_off]) : 0.f;
+            if (VEC) ra[j] = ok ? to_f<T>(r[a_off]) : 0.f;
         }
 #pragma unroll
         for (int j = 0; j < (TOK * COLS + THREADS - 1) / THREADS; ++j) {
@@ -93,6 +101,7 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
             const int at = tt * DPS + (i / E) * ES + i % E;
             qs[at] = SILU ? silu_f(rq[j]) : rq[j];  // silu(0) = 0 keeps the padding zero
             ks[at] = SILU ? silu_f(rk[j]) : rk[j];
+            if (VEC) as[at] = ra[j];
         }
 #pragma unroll
         for (int j = 0; j < (TOK * COLS + THREADS - 1) / THREADS; ++j) {
@@ -106,14 +115,16 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
             const float v = vs[tt * COLS + col];
             const float4* kr = reinterpret_cast<const float4*>(ks + tt * DPS + slice * ES);
             const float4* qr = reinterpret_cast<const float4*>(qs + tt * DPS + slice * ES);
+            const float4* ar = reinterpret_cast<const float4*>(as + (VEC ? tt * DPS + slice * ES : 0));
             float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int e4 = 0; e4 < E / 4; ++e4) {
                 const float4 k4 = kr[e4], q4 = qr[e4];
-                s[4 * e4 + 0] = fmaf(g, s[4 * e4 + 0], k4.x * v);
-                s[4 * e4 + 1] = fmaf(g, s[4 * e4 + 1], k4.y * v);
-                s[4 * e4 + 2] = fmaf(g, s[4 * e4 + 2], k4.z * v);
-                s[4 * e4 + 3] = fmaf(g, s[4 * e4 + 3], k4.w * v);
+                const float4 a4 = VEC ? ar[e4] : make_float4(g, g, g, g);
+                s[4 * e4 + 0] = fmaf(a4.x, s[4 * e4 + 0], k4.x * v);
+                s[4 * e4 + 1] = fmaf(a4.y, s[4 * e4 + 1], k4.y * v);
+                s[4 * e4 + 2] = fmaf(a4.z, s[4 * e4 + 2], k4.z * v);
+                s[4 * e4 + 3] = fmaf(a4.w, s[4 * e4 + 3], k4.w * v);
                 o[0] = fmaf(s[4 * e4 + 0], q4.x, o[0]);
                 o[1] = fmaf(s[4 * e4 + 1], q4.y, o[1]);
                 o[2] = fmaf(s[4 * e4 + 2], q4.z, o[2]);
@@ -165,13 +176,13 @@ __global__ void silu_rows_kernel(const T* __restrict__ x, long long stride, floa
     pdl_trigger();
 }
 
-template <typename T, bool SILU>
+template <typename T, bool SILU, bool VEC = false>
 int launch_scan(const T* proj, long long stride, int q_off, int k_off, int v_off, float* out, float* state,
                 const float* decay, const int* cu, const int* ctx, const int* slots, dim3 grid, int nh, int d, int dv,
-                cudaStream_t stream) {
+                cudaStream_t stream, int a_off = 0) {
     const int e = (d + SLICES - 1) / SLICES;
-#define RLIS_SCAN(E) rlis_launch(lightning_scan_kernel<T, E, SILU>, grid, THREADS, 0, stream, proj, stride, q_off, k_off, \
-                                 v_off, out, state, decay, cu, ctx, slots, nh, d, dv)
+#define RLIS_SCAN(E) rlis_launch(lightning_scan_kernel<T, E, SILU, VEC>, grid, THREADS, 0, stream, proj, stride, q_off, k_off, \
+                                 v_off, out, state, decay, cu, ctx, slots, nh, d, dv, a_off)
     if (e <= 4) RLIS_SCAN(4);
     else if (e <= 8) RLIS_SCAN(8);
     else if (e <= 16) RLIS_SCAN(16);
@@ -211,4 +222,96 @@ extern "C" int rlis_lightning_scan(const void* proj, long long stride, int q_off
         return launch_scan<bf16, true>((const bf16*)proj, stride, q_off, k_off, v_off, out, state, decay, cu_seqlens,
                                        ctx_lens, state_slots, grid, nh, d, dv, stream);
     return RLIS_ERR_UNSUPPORTED;
+}
+
+
+namespace {
+// One row of float32 inputs of a recurrence a token, [q | k | v | a]: nh heads of d (q, k, a) and of dv (v).
+//   q: columns q_off of the projection's row, the first rot_dims entries of every head turned with the entries rot_dims
+//      / 2 further on by the angle position * inv_freq[i]; q_silu: silu(q) (no rotation then)
+//   k: the same rotation, times k_scale; with `lower`: the columns at k_off are the logits z of a forget gate, a = lower +
+//      (1 - lower) sigmoid(z + gate_bias) goes to the fourth segment and k = 1 - a
+//   v: as projected.
+template <typename T>
+__global__ __launch_bounds__(256) void recurrence_inputs_kernel(
+    const T* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, float* __restrict__ out, int nh, int d,
+    int dv, const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ positions, float k_scale,
+    int q_silu, const float* __restrict__ lower, const float* __restrict__ gate_bias) {
+    pdl_wait_and_trigger();
+    const int t = blockIdx.x;
+    const int qk = nh * d, hv = nh * dv;
+    const int width = 2 * qk + hv + (lower != nullptr ? qk : 0);
+    const T* row = proj + (size_t)t * stride;
+    float* orow = out + (size_t)t * width;
+    const int half = rot_dims >> 1;
+    const float pos = rot_dims > 0 ? (float)positions[t] : 0.f;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < 2 * qk + hv; c += gridDim.y * blockDim.x) {
+        if (c >= 2 * qk) {
+            orow[c] = to_f<T>(row[v_off + c - 2 * qk]);
+            continue;
+        }
+        const bool is_q = c < qk;
+        const int hc = is_q ? c : c - qk;                 // head * d + entry
+        const T* x = row + (is_q ? q_off : k_off);
+        float val = to_f<T>(x[hc]);
+        if (!is_q && lower != nullptr) {
+            const float l = lower[hc];
+            const float z = val + (gate_bias != nullptr ? gate_bias[hc] : 0.f);
+            const float a = l + (1.0f - l) * (1.0f / (1.0f + expf(-z)));
+            orow[2 * qk + hv + hc] = a;
+            orow[c] = 1.0f - a;
+            continue;
+        }
+        const int j = hc % d;
+        if (j < rot_dims) {
+            const int pj = j < half ? j + half : j - half;
+            const float other = to_f<T>(x[hc - j + pj]);
+            float sn, cs;
+            sincosf(pos * inv_freq[j < half ? j : pj], &sn, &cs);
+            val = j < half ? rope_first(val, other, cs, sn) : rope_second(other, val, cs, sn);
+        }
+        if (is_q && q_silu) val = silu_f(val);
+        orow[c] = is_q ? val : val * k_scale;
+    }
+}
+}  // namespace
+
+// out float32 [n_tokens, 2 nh d + nh dv (+ nh d with `lower`)]; inv_freq float32 [rot_dims / 2] and positions int32
+// [n_tokens] when rot_dims > 0; lower, gate_bias float32 [nh d] or null.
+extern "C" int rlis_recurrence_inputs(const void* proj, long long stride, int q_off, int k_off, int v_off, float* out,
+                                      int n_tokens, int nh, int d, int dv, const float* inv_freq, int rot_dims,
+                                      const int* positions, float k_scale, int q_silu, const float* lower,
+                                      const float* gate_bias, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (nh <= 0 || d <= 0 || dv <= 0 || rot_dims < 0 || rot_dims > d || (rot_dims & 1) ||
+        (rot_dims > 0 && (inv_freq == nullptr || positions == nullptr)))
+        return RLIS_ERR_UNSUPPORTED;
+    const int cols = 2 * nh * d + nh * dv;
+    const dim3 blocks(n_tokens, (cols + 1023) / 1024 < 8 ? (cols + 1023) / 1024 : 8);
+    if (dtype == RLIS_F32)
+        rlis_launch(recurrence_inputs_kernel<float>, blocks, 256, 0, stream, (const float*)proj, stride, q_off, k_off, v_off,
+                    out, nh, d, dv, inv_freq, rot_dims, positions, k_scale, q_silu, lower, gate_bias);
+    else if (dtype == RLIS_BF16)
+        rlis_launch(recurrence_inputs_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)proj, stride, q_off, k_off, v_off,
+                    out, nh, d, dv, inv_freq, rot_dims, positions, k_scale, q_silu, lower, gate_bias);
+    else
+        return RLIS_ERR_UNSUPPORTED;
+    return RLIS_LAUNCH_CHECK();
+}
+
+// The walk over prepared float32 rows [n_tokens, width]: q, k, v at columns q_off, k_off, v_off; a decay a head
+// (`decay` float32 [nh]) or, with `decay` null, a decay a token and channel at columns a_off.
+extern "C" int rlis_recurrence_scan(const float* rows, long long width, int q_off, int k_off, int v_off, int a_off,
+                                    float* out, float* state, const float* decay, const int* cu_seqlens,
+                                    const int* ctx_lens, const int* state_slots, int n_seqs, int nh, int d, int dv,
+                                    cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (d <= 0 || d > SLICES * MAX_E || dv <= 0 || nh <= 0 || nh > 65535) return RLIS_ERR_UNSUPPORTED;
+    dim3 grid(n_seqs, nh, (dv + COLS - 1) / COLS);
+    if (grid.z > 65535) return RLIS_ERR_UNSUPPORTED;
+    if (decay != nullptr)
+        return launch_scan<float, false, false>(rows, width, q_off, k_off, v_off, out, state, decay, cu_seqlens, ctx_lens,
+                                                state_slots, grid, nh, d, dv, stream);
+    return launch_scan<float, false, true>(rows, width, q_off, k_off, v_off, out, state, nullptr, cu_seqlens, ctx_lens,
+                                           state_slots, grid, nh, d, dv, stream, a_off);
 }

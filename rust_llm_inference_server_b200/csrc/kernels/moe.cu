@@ -5,6 +5,11 @@
 //            extra row of W_r, where given, is the logit of a gate on a shared expert: sigmoid of it.
 //            With `softmax_chosen`: z = W_r h + b_r; the `top` experts with the largest z (+ correction) are
 //            chosen and their weights are the softmax over the chosen logits alone, times route_scale.
+//            scoring 2: s = softmax(z) over all router outputs.  `n_groups` > 1: the outputs form that many
+//            equal groups of neighbours, a group's rank is its largest s + correction, and only outputs of the
+//            `keep_groups` best groups can be chosen.  `normalize`: the chosen s are divided by their sum
+//            (+ 1e-20) before route_scale.  Router outputs from `n_experts` of align and combine on (the last
+//            rows of W_r) are identity experts: they have no matrices, and combine adds weight * x for them.
 //   align:   the (token, choice) pairs are sorted by expert into slots; every expert's run of slots is
 //            padded to a multiple of the row tile (32 rows, or 128 when there are many pairs an expert),
 //            so a tile of rows belongs to one expert.  All on the device: no count ever reaches the
@@ -13,7 +18,8 @@
 //   down:    y[slot, :] = W_down_e act[slot, :]                         (float32)
 //   combine: out[t, :] = sum_k weight[t, k] * y[slot(t, k), :] + shared_gate[t] * shared[t, :]
 //
-// glu(g, u) = g' * sigmoid(slope * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit).
+// glu(g, u) = g' * sigmoid(slope * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit); slope +inf:
+// max(g', 0) * (u' + shift).
 //
 // The products here are CUDA-core FFMA over k = 0..K-1 in that order for every output element, in float32
 // whatever the element type, so a token's result does not depend on what else is in the batch; the
@@ -43,10 +49,11 @@ __global__ __launch_bounds__(1024) void moe_route_kernel(
     const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ correction,
     int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ shared_gate,
     int n_tokens, int width, int n_experts, int top, float route_scale,
-    const float* __restrict__ router_bias, int softmax_chosen) {
+    const float* __restrict__ router_bias, int scoring, int n_groups, int keep_groups, int normalize) {
     pdl_wait_and_trigger();
     extern __shared__ float sm[];
-    const int stride = 2 * n_experts + 1;   // per token: z [n_experts + 1], choice [n_experts]
+    const bool softmax_chosen = scoring == 1;
+    const int stride = 2 * n_experts + 1 + n_groups;   // per token: z [n_experts + 1], choice [n_experts], group ranks
     const int t0 = blockIdx.x * TOK;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int n_rows = n_experts + (shared_gate != nullptr ? 1 : 0);
@@ -92,7 +99,7 @@ __global__ __launch_bounds__(1024) void moe_route_kernel(
         const int i = idx / n_experts, e = idx - i * n_experts;
         float* z = sm + i * stride;
         const float logit = z[e] + (router_bias != nullptr ? router_bias[e] : 0.f);
-        const float s = softmax_chosen ? logit : sigmoidf_(logit);
+        const float s = scoring != 0 ? logit : sigmoidf_(logit);     // (scoring 2: the softmax is taken below)
         z[e] = s;
         z[n_experts + 1 + e] = s + (correction != nullptr ? correction[e] : 0.f);
     }
@@ -104,6 +111,41 @@ __global__ __launch_bounds__(1024) void moe_route_kernel(
         if (t >= n_tokens) break;
         float* z = sm + i * stride;
         float* choice = z + n_experts + 1;
+        if (scoring == 2) {
+            // softmax over all outputs, in float32; the correction joins the choice scores only
+            float mx = -INFINITY;
+            for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, z[e]);
+            mx = warp_max(mx);
+            float sum = 0.f;
+            for (int e = lane; e < n_experts; e += 32) sum += expf(z[e] - mx);
+            sum = warp_sum(sum);
+            for (int e = lane; e < n_experts; e += 32) {
+                const float s = expf(z[e] - mx) / sum;
+                z[e] = s;
+                choice[e] = s + (correction != nullptr ? correction[e] : 0.f);
+            }
+            __syncwarp();
+        }
+        if (n_groups > 1) {
+            // a group's rank is its best choice score; outputs of groups that are not kept cannot be chosen
+            float* rank = choice + n_experts;
+            const int per = n_experts / n_groups;
+            for (int g = lane; g < n_groups; g += 32) {
+                float r = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; ++e) r = fmaxf(r, choice[e]);
+                rank[g] = r;
+            }
+            __syncwarp();
+            // a group is kept when fewer than keep_groups groups rank before it (ties: the lower index first)
+            for (int g = lane; g < n_groups; g += 32) {
+                const float r = rank[g];
+                int before = 0;
+                for (int o = 0; o < n_groups; ++o) before += (rank[o] > r || (rank[o] == r && o < g)) ? 1 : 0;
+                if (before >= keep_groups)
+                    for (int e = g * per; e < (g + 1) * per; ++e) choice[e] = -INFINITY;
+            }
+            __syncwarp();
+        }
         for (int k = 0; k < top; ++k) {
             float best = -INFINITY;
             int at = 0x7fffffff;
@@ -120,7 +162,7 @@ __global__ __launch_bounds__(1024) void moe_route_kernel(
             if (at >= n_experts) at = k;        // scores that compare with nothing (NaN): still a valid index
             if (lane == 0) {
                 top_idx[(size_t)t * top + k] = at;
-                top_w[(size_t)t * top + k] = softmax_chosen ? z[at] : z[at] * route_scale;
+                top_w[(size_t)t * top + k] = (softmax_chosen || normalize) ? z[at] : z[at] * route_scale;
                 choice[at] = -INFINITY;
             }
             __syncwarp();
@@ -136,6 +178,11 @@ __global__ __launch_bounds__(1024) void moe_route_kernel(
                 sum += e;
             }
             for (int k = 0; k < top; ++k) wt[k] = wt[k] / sum * route_scale;
+        } else if (normalize && lane == 0) {
+            float* wt = top_w + (size_t)t * top;
+            float sum = 0.f;
+            for (int k = 0; k < top; ++k) sum += wt[k];
+            for (int k = 0; k < top; ++k) wt[k] = wt[k] / (sum + 1e-20f) * route_scale;
         }
     }
 }
@@ -256,7 +303,7 @@ __global__ __launch_bounds__(256) void moe_gemm_kernel(
             if (GLU) {
                 const float g = fminf(accg[i][j], limit);
                 const float u = fminf(fmaxf(accu[i][j], -limit), limit);
-                ((T*)out_)[orow + gn] = from_f<T>(g * sigmoidf_(slope * g) * (u + shift));
+                ((T*)out_)[orow + gn] = from_f<T>(glu_gate(g, slope) * (u + shift));
             } else {
                 ((float*)out_)[orow + gn] = accg[i][j];
             }
@@ -268,7 +315,8 @@ __global__ __launch_bounds__(256) void moe_gemm_kernel(
 template <typename T>
 __global__ __launch_bounds__(256) void moe_combine_kernel(
     const float* __restrict__ y, const int* __restrict__ pair_slot, const float* __restrict__ top_w,
-    const T* __restrict__ shared, const float* __restrict__ shared_gate, T* __restrict__ out, int width, int top) {
+    const T* __restrict__ shared, const float* __restrict__ shared_gate, T* __restrict__ out, int width, int top,
+    const T* __restrict__ x, const int* __restrict__ top_idx, int n_experts) {
     pdl_wait_and_trigger();
     const int t = blockIdx.x;
     const float sg = shared_gate != nullptr ? shared_gate[t] : 1.0f;
@@ -278,9 +326,11 @@ __global__ __launch_bounds__(256) void moe_combine_kernel(
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int k = 0; k < top; ++k) {
                 const int slot = pair_slot[(size_t)t * top + k];
-                if (slot < 0) continue;
+                const bool same = slot < 0 && x != nullptr && top_idx[(size_t)t * top + k] >= n_experts;   // an identity expert
+                if (slot < 0 && !same) continue;
                 const float w = top_w[(size_t)t * top + k];
-                const float4 v = *reinterpret_cast<const float4*>(y + (size_t)slot * width + c);
+                const float4 v = same ? load4(x + (size_t)t * width + c)
+                                      : *reinterpret_cast<const float4*>(y + (size_t)slot * width + c);
                 acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y);
                 acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
             }
@@ -299,6 +349,8 @@ __global__ __launch_bounds__(256) void moe_combine_kernel(
         for (int k = 0; k < top; ++k) {
             const int slot = pair_slot[(size_t)t * top + k];
             if (slot >= 0) acc = fmaf(top_w[(size_t)t * top + k], y[(size_t)slot * width + c], acc);
+            else if (x != nullptr && top_idx[(size_t)t * top + k] >= n_experts)
+                acc = fmaf(top_w[(size_t)t * top + k], to_f<T>(x[(size_t)t * width + c]), acc);
         }
         if (shared != nullptr) acc = fmaf(sg, to_f<T>(shared[(size_t)t * width + c]), acc);
         out[(size_t)t * width + c] = from_f<T>(acc);
@@ -319,30 +371,33 @@ __global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, in
     const size_t ui = interleave > 0 ? gi + interleave : (size_t)inter + i;
     const float g = fminf(to_f<T>(gu[t * 2 * inter + gi]), limit);
     const float u = fminf(fmaxf(to_f<T>(gu[t * 2 * inter + ui]), -limit), limit);
-    out[idx] = from_f<T>(g * sigmoidf_(slope * g) * (u + shift));
+    out[idx] = from_f<T>(glu_gate(g, slope) * (u + shift));
 }
 }  // namespace
 
 
 // x [T, width] in the element type; w_router float32 [n_experts (+ 1 with shared_gate), width];
 // correction float32 [n_experts] or null; top_idx int32 [T, top]; top_w float32 [T, top]; shared_gate
-// float32 [T] or null.
+// float32 [T] or null.  scoring 0: sigmoid; 1: softmax over the chosen logits; 2: softmax over all outputs.
 extern "C" int rlis_moe_route(const void* x, const float* w_router, const float* correction, int* top_idx,
                               float* top_w, float* shared_gate, int n_tokens, int width, int n_experts, int top,
-                              float route_scale, const float* router_bias, int softmax_chosen, int dtype,
-                              cudaStream_t stream) {
+                              float route_scale, const float* router_bias, int scoring, int n_groups, int keep_groups,
+                              int normalize, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 512) return RLIS_ERR_UNSUPPORTED;
+    if (n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 512 || scoring < 0 || scoring > 2) return RLIS_ERR_UNSUPPORTED;
+    if (n_groups < 1 || n_experts % n_groups != 0 || keep_groups < 1 || keep_groups > n_groups ||
+        top > keep_groups * (n_experts / n_groups) || (scoring == 2 && shared_gate != nullptr))
+        return RLIS_ERR_UNSUPPORTED;
     // eight tokens a CTA when there are many (the router matrix is then read an eighth as often), one otherwise
     const int tok = n_tokens >= 64 ? 8 : 1;
-    const size_t smem = (size_t)tok * (2 * n_experts + 1) * sizeof(float);
+    const size_t smem = (size_t)tok * (2 * n_experts + 1 + n_groups) * sizeof(float);
     if (smem > 48 * 1024) return RLIS_ERR_UNSUPPORTED;
     const unsigned blocks = (unsigned)((n_tokens + tok - 1) / tok);
     const int rows = n_experts + (shared_gate != nullptr ? 1 : 0);
     const unsigned threads = 32u * (unsigned)(rows < 32 ? (rows < tok ? tok : rows) : 32);
 #define RLIS_ROUTE(T, TOK) rlis_launch(moe_route_kernel<T, TOK>, blocks, threads, smem, stream, (const T*)x, w_router, correction, \
                                        top_idx, top_w, shared_gate, n_tokens, width, n_experts, top, route_scale, \
-                                       router_bias, softmax_chosen)
+                                       router_bias, scoring, n_groups, keep_groups, normalize)
     if (dtype == RLIS_F32) { if (tok == 8) RLIS_ROUTE(float, 8); else RLIS_ROUTE(float, 1); }
     else if (dtype == RLIS_BF16) { if (tok == 8) RLIS_ROUTE(bf16, 8); else RLIS_ROUTE(bf16, 1); }
     else return RLIS_ERR_UNSUPPORTED;
@@ -416,15 +471,15 @@ extern "C" int rlis_moe_gather_rows(const void* x, void* out, const int* sorted_
 }
 
 extern "C" int rlis_moe_combine(const float* y, const int* pair_slot, const float* top_w, const void* shared,
-                                const float* shared_gate, void* out, int n_tokens, int width, int top, int dtype,
-                                cudaStream_t stream) {
+                                const float* shared_gate, void* out, int n_tokens, int width, int top, const void* x,
+                                const int* top_idx, int n_experts, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dtype == RLIS_F32)
         rlis_launch(moe_combine_kernel<float>, n_tokens, 256, 0, stream, y, pair_slot, top_w, (const float*)shared,
-                    shared_gate, (float*)out, width, top);
+                    shared_gate, (float*)out, width, top, (const float*)x, top_idx, n_experts);
     else if (dtype == RLIS_BF16)
         rlis_launch(moe_combine_kernel<bf16>, n_tokens, 256, 0, stream, y, pair_slot, top_w, (const bf16*)shared,
-                    shared_gate, (bf16*)out, width, top);
+                    shared_gate, (bf16*)out, width, top, (const bf16*)x, top_idx, n_experts);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

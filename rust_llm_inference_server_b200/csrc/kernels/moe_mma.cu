@@ -139,7 +139,7 @@ __global__ __launch_bounds__(TM == 128 ? 256 : TM * 4) void moe_mma_kernel(
                 if (GLU) {
                     const float gg = fminf(vg, limit);
                     const float uu = fminf(fmaxf(accu[m][nt][half * 2 + j], -limit), limit);
-                    ((bf16*)out_)[orow + gn] = __float2bfloat16_rn(gg / (1.0f + expf(-slope * gg)) * (uu + shift));
+                    ((bf16*)out_)[orow + gn] = __float2bfloat16_rn(glu_gate(gg, slope) * (uu + shift));
                 } else {
                     ((float*)out_)[orow + gn] = vg;
                 }

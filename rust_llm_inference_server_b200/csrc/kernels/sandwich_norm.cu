@@ -181,7 +181,7 @@ __global__ __launch_bounds__(128) void head_norm_gate_kernel(
     const T* g = gate != nullptr ? gate + (size_t)t * gate_stride + (size_t)h * dv : nullptr;
     T* o = out + (size_t)unit * dv;
     for (int c = lane; c < dv; c += 32) {
-        float y = xr[c] * r * w[c];
+        float y = xr[c] * r * (w != nullptr ? w[c] : 1.0f);
         if (g != nullptr) {
             const float z = to_f<T>(g[c]);
             const float sg = 1.0f / (1.0f + expf(-z));

@@ -310,15 +310,16 @@ def sum_norm(resid: torch.Tensor | None, alpha: float, branches, w_out: torch.Te
 GATE_ACTIVATIONS = {"sigmoid": 0, "silu": 1}
 
 
-def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, n_heads: int,
+def head_norm_gate(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out: torch.Tensor, n_heads: int,
                    gate: torch.Tensor | None = None, activation: str = "sigmoid") -> torch.Tensor:
     """out[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * weight * act(gate[t, h, :]): one norm a head,
-    one weight vector [dv] for all heads.  x float32 [T, nh dv]; gate [T, nh dv] in out's type (may be a column
+    one weight vector [dv] for all heads (None: no weight).  x float32 [T, nh dv]; gate [T, nh dv] in out's type (may be a column
     slice of wider rows); activation "sigmoid" or "silu"."""
     T, W = x.shape
     dv = W // n_heads
     _req(x, "x", torch.float32, (T, n_heads * dv))
-    _req(weight, "weight", torch.float32, (dv,))
+    if weight is not None:
+        _req(weight, "weight", torch.float32, (dv,))
     _req(out, "out", None, (T, W))
     gp, gs = None, 0
     if gate is not None:
@@ -327,7 +328,8 @@ def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch
         gp, gs = gate.data_ptr(), gate.stride(0)
     if activation not in GATE_ACTIVATIONS:
         raise KernelError(f"head_norm_gate: unknown activation {activation!r}; known: {sorted(GATE_ACTIVATIONS)}")
-    check(lib().rlis_head_norm_gate(x.data_ptr(), weight.data_ptr(), gp, gs, out.data_ptr(), T, n_heads, dv, float(eps),
+    check(lib().rlis_head_norm_gate(x.data_ptr(), weight.data_ptr() if weight is not None else None, gp, gs, out.data_ptr(),
+                                    T, n_heads, dv, float(eps),
                                     GATE_ACTIVATIONS[activation], _code(out.dtype), _stream()), "head_norm_gate")
     _count("head_norm_gate")
     return out
@@ -590,6 +592,63 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: 
                                     dv, _code(proj.dtype), activated.data_ptr() if activated is not None else None,
                                     T, _stream()), "lightning_scan")
     _count("lightning_scan" + (".silu_pass" if activated is not None else ""))
+    return out
+
+
+def recurrence_inputs(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor, n_heads: int, d: int,
+                      dv: int, rotation: tuple | None = None, positions: torch.Tensor | None = None,
+                      k_scale: float = 1.0, q_silu: bool = False, lower: torch.Tensor | None = None,
+                      gate_bias: torch.Tensor | None = None) -> torch.Tensor:
+    """The float32 inputs of a linear recurrence, one row [q | k | v (| a)] a token, from the rows of a stacked
+    projection `proj` [T, N] (queries at column q_off, keys at k_off: n_heads heads of d; values at v_off: heads of
+    dv).  `rotation` = (float32 frequencies [r / 2], r): entry i < r / 2 of every query and key head turns with
+    entry i + r / 2 by the angle positions[t] * frequency i.  Keys are multiplied by `k_scale`; `q_silu`: q =
+    silu(q).  `lower` (float32 [n_heads d]): the columns at k_off are the logits z of a forget gate a = lower + (1 -
+    lower) sigmoid(z + gate_bias); the row then holds k = 1 - a and, as a fourth segment, a."""
+    T, N = proj.shape
+    qk, hv = n_heads * d, n_heads * dv
+    _req(proj, "proj")
+    _req(out, "out", torch.float32, (T, 2 * qk + hv + (qk if lower is not None else 0)))
+    if max(q_off, k_off) + qk > N or v_off + hv > N:
+        raise KernelError("recurrence_inputs: the column offsets reach beyond the projection's rows")
+    inv_freq, rot_dims = rotation if rotation is not None else (None, 0)
+    if rot_dims:
+        _req(inv_freq, "rotation frequencies", torch.float32, (rot_dims // 2,))
+        _req(positions, "positions", torch.int32, (T,))
+        if rot_dims % 2 or rot_dims > d or q_silu or lower is not None:
+            raise KernelError(f"recurrence_inputs: {rot_dims} rotated entries do not fit plain heads of {d} in pairs")
+    for v, nm in ((lower, "lower"), (gate_bias, "gate_bias")):
+        if v is not None:
+            _req(v, nm, torch.float32, (qk,))
+    check(lib().rlis_recurrence_inputs(proj.data_ptr(), proj.stride(0), int(q_off), int(k_off), int(v_off), out.data_ptr(),
+                                       T, n_heads, d, dv, inv_freq.data_ptr() if rot_dims else None, int(rot_dims),
+                                       positions.data_ptr() if rot_dims else None, float(k_scale), 1 if q_silu else 0,
+                                       lower.data_ptr() if lower is not None else None,
+                                       gate_bias.data_ptr() if gate_bias is not None else None, _code(proj.dtype),
+                                       _stream()), "recurrence_inputs")
+    _count("recurrence_inputs" + (".rot" if rot_dims else "") + (".gate" if lower is not None else ""))
+    return out
+
+
+def recurrence_scan(rows: torch.Tensor, out: torch.Tensor, state: torch.Tensor, decay: torch.Tensor | None, step,
+                    n_heads: int, d: int, dv: int) -> torch.Tensor:
+    """The linear recurrence over the step's tokens from prepared float32 rows [T, q | k | v (| a)] (see
+    `recurrence_inputs`): per request and head S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t, with a_t = decay[head]
+    for every channel (`decay` float32 [n_heads]) or, with `decay` None, the rows' fourth segment.  `state` float32
+    [slots, nh, dv, d] holds S, transposed, between steps (a request whose first token is in this step starts from
+    zero); out float32 [T, nh dv]."""
+    T, W = rows.shape
+    qk, hv = n_heads * d, n_heads * dv
+    _req(rows, "rows", torch.float32, (T, 2 * qk + hv + (qk if decay is None else 0)))
+    _req(out, "out", torch.float32, (T, hv))
+    _req(state, "state", torch.float32, (None, n_heads, dv, d))
+    if decay is not None:
+        _req(decay, "decay", torch.float32, (n_heads,))
+    check(lib().rlis_recurrence_scan(rows.data_ptr(), W, 0, qk, 2 * qk, 2 * qk + hv, out.data_ptr(), state.data_ptr(),
+                                     decay.data_ptr() if decay is not None else None, step.cu_seqlens.data_ptr(),
+                                     step.ctx_lens.data_ptr(), step.state_slots.data_ptr(), step.n_seqs, n_heads, d, dv,
+                                     _stream()), "recurrence_scan")
+    _count("recurrence_scan" + (".channel_decay" if decay is None else ""))
     return out
 
 
@@ -1079,7 +1138,7 @@ def attention(q, k_cache, v_cache, out, step, group: int, n_heads: int, n_kv_hea
 def glu_act(gate_up: torch.Tensor, out: torch.Tensor, slope: float = 1.0, limit: float | None = None,
             up_shift: float = 0.0, interleave: int = 0) -> torch.Tensor:
     """out[t, i] = g sigmoid(slope g) (u + up_shift) with g = gate_up[t, i] and u = gate_up[t, I + i], both in
-    float32; with a `limit`, g is cut at limit from above and u clipped to [-limit, limit] first.
+    float32 (slope +inf: max(g, 0) (u + up_shift)); with a `limit`, g is cut at limit from above and u clipped to [-limit, limit] first.
     interleave B > 0: blocks of B gate columns each followed by their B columns of u."""
     T, I2 = gate_up.shape
     if I2 % 2:
@@ -1096,7 +1155,8 @@ def glu_act(gate_up: torch.Tensor, out: torch.Tensor, slope: float = 1.0, limit:
 def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w, k_w, eps: float, v_other, lam: float,
                   q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slots, n_heads: int,
                   n_kv_heads: int, dim: int, v_dim: int, page_size: int, rotation: tuple | None = None,
-                  positions: torch.Tensor | None = None, q_temp: tuple | None = None) -> torch.Tensor:
+                  positions: torch.Tensor | None = None, q_temp: tuple | None = None, rot_half: bool = False,
+                  proj_bias: torch.Tensor | None = None) -> torch.Tensor:
     """From the rows of a stacked projection `proj` [T, N] (queries at column q_off, keys at k_off, values
     at v_off): q_out [T, nh dim] = per-head rmsnorm(q) * q_w, and at `slots` of the paged caches the keys
     rmsnorm(k) * k_w and the values, mixed as (1 - lam) v + lam v_other where `v_other` (a [T, nkv v_dim]
@@ -1107,7 +1167,8 @@ def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w, k
     query and key head, i < r / 2, turn by the angle position * frequency i, cos and sin times the multiplier
     (values are taken as projected, so v_off = k_off caches the unrotated keys as values).  `q_temp` = (coef,
     every): queries are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1) at position p.  Both take
-    `positions` (int32 [T])."""
+    `positions` (int32 [T]).  `rot_half`: entry i turns with entry i + r / 2 instead of its neighbour.  `proj_bias`
+    (float32 [N]): added to the queries, keys and values as they are read from `proj`."""
     T, N = proj.shape
     _req(proj, "proj")
     _req(q_out, "q_out", proj.dtype, (T, n_heads * dim))
@@ -1134,6 +1195,8 @@ def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w, k
     coef, every = q_temp if q_temp is not None else (0.0, 0)
     if rot_dims or every:
         _req(positions, "positions", torch.int32, (T,))
+    if proj_bias is not None:
+        _req(proj_bias, "proj_bias", torch.float32, (N,))
     check(lib().rlis_qk_norm_store(proj.data_ptr(), N, int(q_off), int(k_off), int(v_off),
                                    q_w.data_ptr() if q_w is not None else None,
                                    k_w.data_ptr() if k_w is not None else None, float(eps), vo, vo_stride, float(lam),
@@ -1142,6 +1205,7 @@ def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w, k
                                    slots.data_ptr() if slots is not None else None, T, n_heads, n_kv_heads, dim, v_dim,
                                    page_size, inv_freq.data_ptr() if rot_dims else None, int(rot_dims), float(rot_mag),
                                    positions.data_ptr() if (rot_dims or every) else None, float(coef), int(every),
+                                   1 if rot_half else 0, proj_bias.data_ptr() if proj_bias is not None else None,
                                    _code(proj.dtype), _stream()), "qk_norm_store")
     _count("qk_norm_store" + (".mix" if v_other is not None else "") + (".rot" if rot_dims else ""))
     return q_out
@@ -1195,11 +1259,14 @@ def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_h
     if bias is not None:
         _req(bias, "bias", torch.float32, (None, n_heads))
         n_dist, bp = bias.shape[0], bias.data_ptr()
-    gp, gs = None, 0
+    gp, gs, gc = None, 0, 1
     if gate is not None:
-        if gate.dtype != q.dtype or tuple(gate.shape) != (T, n_heads) or gate.stride(1) != 1 or not gate.is_cuda:
-            raise KernelError("attention_biased: the gate must be [T, nh] rows with unit stride in q's type")
+        # one logit a head, or one a channel of every head
+        if (gate.dtype != q.dtype or tuple(gate.shape) not in ((T, n_heads), (T, n_heads * v_dim)) or gate.stride(1) != 1
+                or not gate.is_cuda):
+            raise KernelError("attention_biased: the gate must be [T, nh] or [T, nh v_dim] rows with unit stride in q's type")
         gp, gs = gate.data_ptr(), gate.stride(0)
+        gc = v_dim if gate.shape[1] == n_heads * v_dim and v_dim > 1 else 1
     for v, nm in ((sinks, "sinks"), (slopes, "slopes")):
         if v is not None:
             _req(v, nm, torch.float32, (n_heads,))
@@ -1216,14 +1283,14 @@ def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_h
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
             scratch.data_ptr() if scratch is not None else None, bp, n_dist, gp, gs, step.dec_rows.data_ptr(),
             step.dec_seqs.data_ptr(), step.ctx_lens.data_ptr(), tables.data_ptr(), tables.shape[1], n_dec, n_heads,
-            n_kv_heads, dim, v_dim, page_size, float(scale), int(window), pieces, sp, lp, _stream()), "attention_bias_decode")
+            n_kv_heads, dim, v_dim, page_size, float(scale), int(window), pieces, sp, lp, gc, _stream()), "attention_bias_decode")
         _count("attention_bias.decode.mma" + (".split" if pieces > 1 else ""))
     if n_tiles:
         check(lib().rlis_attention_bias_prefill(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), bp, n_dist, gp, gs,
             step.prefill_tiles.data_ptr(), n_tiles, step.cu_seqlens.data_ptr(), step.ctx_lens.data_ptr(),
             tables.data_ptr(), tables.shape[1], n_heads, n_kv_heads, dim, v_dim, page_size, float(scale), int(window),
-            sp, lp, _stream()), "attention_bias_prefill")
+            sp, lp, gc, _stream()), "attention_bias_prefill")
         _count("attention_bias.prefill.mma")
     # what the tensor-core kernels did not take: nothing, the portions only, the single tokens only, or everything
     rows, n_rows = None, T
@@ -1240,7 +1307,7 @@ def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_h
     check(lib().rlis_attention_bias(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), bp, n_dist, gp,
                                     gs, step.seq_of_token.data_ptr(), step.positions.data_ptr(), tables.data_ptr(),
                                     rows.data_ptr() if rows is not None else None, tables.shape[1], n_rows, n_heads,
-                                    n_kv_heads, dim, v_dim, page_size, float(scale), int(window), sp, lp,
+                                    n_kv_heads, dim, v_dim, page_size, float(scale), int(window), sp, lp, gc,
                                     _code(q.dtype), _stream()), "attention_bias")
     _count("attention_bias")
     return out
@@ -1283,13 +1350,23 @@ def _moe_gemm(a, wg_ptr: int, wu_ptr, w_stride: int, interleave: int, out, plan,
 
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: int, top: int, route_scale: float,
               shared_gate: bool, step, router_bias: torch.Tensor | None = None,
-              softmax_chosen: bool = False) -> MoePlan:
+              softmax_chosen: bool = False, scoring: str | None = None, groups: tuple | None = None,
+              normalize: bool = False, n_identity: int = 0) -> MoePlan:
     """Scores s = sigmoid(w_router x + router_bias) in float32; the `top` experts with the largest s +
     correction; weights s * route_scale.  `softmax_chosen`: the logits themselves are the scores, and the
     weights are the softmax over the chosen logits alone (times route_scale).  w_router float32 [n_experts (+ 1), width]: with `shared_gate` its last row is the logit
-    of the shared expert's gate.  Then the pairs are sorted by expert on the device."""
+    of the shared expert's gate.  Then the pairs are sorted by expert on the device.
+
+    `scoring` "softmax": s = softmax over all router outputs.  `n_identity`: the router has that many more outputs
+    after the experts' (identity experts: they return their input, see `moe_combine`), which are scored and chosen
+    like the rest.  `groups` = (count, keep): the outputs form `count` equal groups of neighbours, ranked by their
+    largest s + correction, and only outputs of the `keep` best groups can be chosen.  `normalize`: the chosen
+    scores are divided by their sum (+ 1e-20) before route_scale."""
     T, W = x.shape
     _req(x, "x")
+    n_real, n_experts = n_experts, n_experts + int(n_identity)          # the kernel scores outputs; only experts get slots
+    mode = {None: 1 if softmax_chosen else 0, "sigmoid": 0, "softmax_chosen": 1, "softmax": 2}[scoring]
+    n_groups, keep = groups if groups is not None else (1, 1)
     rows = n_experts + (1 if shared_gate else 0)
     _req(w_router, "w_router", torch.float32, (rows, W))
     if correction is not None:
@@ -1297,8 +1374,8 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: in
     if router_bias is not None:
         _req(router_bias, "router_bias", torch.float32, (n_experts,))
     pairs = T * top
-    tile = moe_tile_rows(pairs, n_experts)
-    max_tiles = min(pairs, n_experts) + pairs // tile      # every expert in use ends in at most one partial tile
+    tile = moe_tile_rows(pairs, n_real)
+    max_tiles = min(pairs, n_real) + pairs // tile         # every expert in use ends in at most one partial tile
     ints = step.buffer("moe_ints", (2 * pairs + max_tiles * tile + max_tiles + 1,), torch.int32)
     flts = step.buffer("moe_floats", (pairs + T,), torch.float32)
     top_idx, pair_slot = ints[:pairs], ints[pairs:2 * pairs]
@@ -1308,13 +1385,13 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: in
     check(lib().rlis_moe_route(x.data_ptr(), w_router.data_ptr(), correction.data_ptr() if correction is not None else None,
                                top_idx.data_ptr(), top_w.data_ptr(), gate.data_ptr() if shared_gate else None, T, W,
                                n_experts, top, float(route_scale),
-                               router_bias.data_ptr() if router_bias is not None else None, 1 if softmax_chosen else 0,
-                               _code(x.dtype), _stream()), "moe_route")
+                               router_bias.data_ptr() if router_bias is not None else None, mode, int(n_groups), int(keep),
+                               1 if normalize else 0, _code(x.dtype), _stream()), "moe_route")
     _count("moe_route")
     check(lib().rlis_moe_align(top_idx.data_ptr(), sorted_pair.data_ptr(), pair_slot.data_ptr(), tile_expert.data_ptr(),
-                               pairs, n_experts, max_tiles, tile, _stream()), "moe_align")
+                               pairs, n_real, max_tiles, tile, _stream()), "moe_align")
     _count("moe_align")
-    return MoePlan(n_tokens=T, top=top, n_experts=n_experts, tile=tile, max_tiles=max_tiles, top_idx=top_idx,
+    return MoePlan(n_tokens=T, top=top, n_experts=n_real, n_identity=int(n_identity), tile=tile, max_tiles=max_tiles, top_idx=top_idx,
                    top_w=top_w, pair_slot=pair_slot, sorted_pair=sorted_pair, tile_expert=tile_expert,
                    shared_gate=gate if shared_gate else None)
 
@@ -1398,10 +1475,15 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan, step) -> to
     return y
 
 
-def moe_combine(y: torch.Tensor, plan: MoePlan, shared, out: torch.Tensor) -> torch.Tensor:
+def moe_combine(y: torch.Tensor, plan: MoePlan, shared, out: torch.Tensor, x: torch.Tensor | None = None) -> torch.Tensor:
     """out[t] = sum over a token's choices of weight * y[slot] (+ gate[t] * shared[t], gate 1 without one),
-    summed in float32 in the order of the choices."""
+    summed in float32 in the order of the choices.  A choice beyond the experts (an identity expert of the plan)
+    adds weight * x[t]; `x` [T, W] is then the feed-forward's input."""
     T, W = out.shape
+    if getattr(plan, "n_identity", 0):
+        _req(x, "x", out.dtype, (T, W))
+    else:
+        x = None
     _req(y, "y", torch.float32, (None, W))
     _req(out, "out")
     if shared is not None:
@@ -1409,7 +1491,8 @@ def moe_combine(y: torch.Tensor, plan: MoePlan, shared, out: torch.Tensor) -> to
     check(lib().rlis_moe_combine(y.data_ptr(), plan.pair_slot.data_ptr(), plan.top_w.data_ptr(),
                                  shared.data_ptr() if shared is not None else None,
                                  plan.shared_gate.data_ptr() if plan.shared_gate is not None else None, out.data_ptr(),
-                                 T, W, plan.top, _code(out.dtype), _stream()), "moe_combine")
+                                 T, W, plan.top, x.data_ptr() if x is not None else None, plan.top_idx.data_ptr(),
+                                 plan.n_experts, _code(out.dtype), _stream()), "moe_combine")
     _count("moe_combine")
     return out
 

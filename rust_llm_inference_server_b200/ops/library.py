@@ -43,19 +43,21 @@ SIGNATURES = {
     "rlis_attention_latent_prefill": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
     "rlis_attention_latent_decode": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_lightning_scan": [P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P, I, P],
-    "rlis_qk_norm_store": [P, LL, I, I, I, P, P, F, P, LL, F, P, P, P, P, I, I, I, I, I, I, P, I, F, P, F, I, I, P],
-    "rlis_attention_bias": [P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, P],
+    "rlis_recurrence_inputs": [P, LL, I, I, I, P, I, I, I, I, P, I, P, F, I, P, P, I, P],
+    "rlis_recurrence_scan": [P, LL, I, I, I, I, P, P, P, P, P, P, I, I, I, I, P],
+    "rlis_qk_norm_store": [P, LL, I, I, I, P, P, F, P, LL, F, P, P, P, P, I, I, I, I, I, I, P, I, F, P, F, I, I, P, I, P],
+    "rlis_attention_bias": [P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, I, P],
     "rlis_attention_bias_mma_takes": [I, I],
-    "rlis_attention_bias_prefill": [P, P, P, P, P, I, P, LL, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P, P],
-    "rlis_attention_bias_decode": [P, P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P],
-    "rlis_moe_route": [P, P, P, P, P, P, I, I, I, I, F, P, I, I, P],
+    "rlis_attention_bias_prefill": [P, P, P, P, P, I, P, LL, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P],
+    "rlis_attention_bias_decode": [P, P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, I, P],
+    "rlis_moe_route": [P, P, P, P, P, P, I, I, I, I, F, P, I, I, I, I, I, P],
     "rlis_moe_align": [P, P, P, P, I, I, I, I, P],
     "rlis_moe_gemm": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, LL, I, I, P],
     "rlis_moe_gather_rows": [P, P, P, I, I, I, I, P],
     "rlis_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, P, I, F, F, F, P],
     "rlis_moe_gemm_mma": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, LL, I, P],
     "rlis_moe_mma_takes_tile": [I],
-    "rlis_moe_combine": [P, P, P, P, P, P, I, I, I, I, P],
+    "rlis_moe_combine": [P, P, P, P, P, P, I, I, I, P, P, I, I, P],
     "rlis_glu_act": [P, P, I, I, F, F, F, I, I, P],
     "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "rlis_attention_generic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],

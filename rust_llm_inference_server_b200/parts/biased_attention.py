@@ -75,11 +75,14 @@ class BiasedAttention(Mixer):
         self.lam = 0.0
         self.bias = self.q_w = self.k_w = self.sinks = self.slopes = None
         self.rotation = None
+        self.rot_half = False
         if spec.rotation is not None:
             pos = build_position(spec.rotation, dtype, device)
-            if getattr(pos, "pairing", None) != "adjacent" or not hasattr(pos, "rotation"):
-                raise ValueError("this mixer rotates entry 2i with entry 2i + 1 (a rotary spec with pairing 'adjacent')")
+            if getattr(pos, "pairing", None) not in ("adjacent", "half") or not hasattr(pos, "rotation"):
+                raise ValueError("this mixer rotates entry 2i with entry 2i + 1 or entry i with entry i + dims / 2 "
+                                 "(a rotary spec with pairing 'adjacent' or 'half')")
             self.rotation = pos.rotation()
+            self.rot_half = pos.pairing == "half"
             if self.rotation[1] > spec.dim:
                 raise ValueError(f"the rotation covers {self.rotation[1]} entries, a head has {spec.dim}")
         if spec.unit_norm and (spec.q_norm is not None or spec.k_norm is not None):
@@ -96,6 +99,10 @@ class BiasedAttention(Mixer):
             self.slopes = torch.tensor([float(v) for v in spec.slopes], dtype=torch.float64).to(torch.float32).to(device)
         if spec.unit_norm:
             self.q_w = self.k_w = torch.ones((spec.dim,), dtype=torch.float32, device=device)
+        if spec.out_gate is not None and spec.head_gate is not None:
+            raise ValueError("a head's output is gated as a whole or channel by channel, not both")
+        self.gate_cols = spec.n_heads * spec.v_dim if spec.out_gate is not None else spec.n_heads
+        self.proj_bias = None
 
     def tensors(self) -> dict:
         s = self.spec
@@ -113,6 +120,11 @@ class BiasedAttention(Mixer):
             out[s.bias.table] = (s.bias.rows, s.n_heads)
         if s.head_gate is not None:
             out[s.head_gate] = (s.n_heads, s.hidden)
+        if s.out_gate is not None:
+            out[s.out_gate] = (s.n_heads * s.v_dim, s.hidden)
+        for name, rows in ((s.q_bias, s.n_heads * s.dim), (s.k_bias, s.n_kv_heads * s.dim), (s.v_bias, s.n_kv_heads * s.v_dim)):
+            if name is not None:
+                out[name] = (rows,)
         if s.value_mix is not None:
             out[s.value_mix] = ()
         return out
@@ -122,12 +134,24 @@ class BiasedAttention(Mixer):
         parts = [src.get(s.q_proj), src.get(s.k_proj)] + ([src.get(s.v_proj)] if s.v_proj is not None else [])
         if s.head_gate is not None:
             parts.append(src.get(s.head_gate))
+        if s.out_gate is not None:
+            parts.append(src.get(s.out_gate))
         w = torch.cat(parts, dim=0)
         pad = -w.shape[0] % 8             # rows of the stacked projection stay 16-byte multiples
         if pad:
             w = torch.cat([w, w.new_zeros((pad, w.shape[1]))], dim=0)
         self.w_in = w.contiguous()
         self.w_o = src.get(s.o_proj).contiguous()
+        if s.q_bias is not None or s.k_bias is not None or s.v_bias is not None:
+            if s.v_proj is None and s.v_bias is not None:
+                raise ValueError("keys that double as values have no value bias")
+            # one float32 entry a column of the stacked projection's row; the kernel that reads q, k and v adds it
+            bias = torch.zeros((self.w_in.shape[0],), dtype=torch.float32, device=self.w_in.device)
+            for name, off in ((s.q_bias, self.q_off), (s.k_bias, self.k_off), (s.v_bias, self.v_off)):
+                if name is not None:
+                    b = src.get(name, "vector")
+                    bias[off:off + b.shape[0]] = b
+            self.proj_bias = bias.contiguous()
         if not s.unit_norm:
             self.q_w = src.get(s.q_norm, "vector").contiguous() if s.q_norm is not None else None
             self.k_w = src.get(s.k_norm, "vector").contiguous() if s.k_norm is not None else None
@@ -173,9 +197,10 @@ class BiasedAttention(Mixer):
             ops.qk_norm_store(proj, self.q_off, self.k_off, self.v_off, self.q_w, self.k_w, self.eps, other, self.lam, q,
                               cache.k, cache.v, step.slots[cache.group] if writes_cache else None, s.n_heads,
                               s.n_kv_heads, s.dim, s.v_dim, cache.page_size, rotation=self.rotation,
-                              positions=step.positions, q_temp=self.q_temp)
+                              positions=step.positions, q_temp=self.q_temp, rot_half=self.rot_half,
+                              proj_bias=self.proj_bias)
         o = step.buffer("attn_o", (T, s.n_heads * s.v_dim), self.dtype)
-        gate = proj[:, self.g_off:self.g_off + s.n_heads] if s.head_gate is not None else None
+        gate = proj[:, self.g_off:self.g_off + self.gate_cols] if (s.head_gate is not None or s.out_gate is not None) else None
         with span("attention"):
             ops.attention_biased(q, cache.k, cache.v, o, self.bias, gate, step, cache.group, s.n_heads, s.n_kv_heads,
                                  s.dim, s.v_dim, cache.page_size, self.scale, self.window, sinks=self.sinks,

@@ -23,11 +23,12 @@ class PreNormBlock:
     def __init__(self, spec, dtype, device):
         self.norm1 = build_norm(spec.norm1, dtype, device)
         self.mixer = build_mixer(spec.mixer, dtype, device)
-        self.norm2 = build_norm(spec.norm2, dtype, device)
-        self.feed_forward = build_feed_forward(spec.feed_forward, dtype, device)
+        # a layer may have no feed-forward: its mixer's result is then the block's pending addition
+        self.feed_forward = build_feed_forward(spec.feed_forward, dtype, device) if spec.feed_forward is not None else None
+        self.norm2 = build_norm(spec.norm2, dtype, device) if self.feed_forward is not None else None
 
     def parts(self):
-        return (self.norm1, self.mixer, self.norm2, self.feed_forward)
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None)
 
     chains_norms = True      # `forward` takes `next_block`
 
@@ -38,6 +39,11 @@ class PreNormBlock:
 
     def forward(self, resid, pending, step, cache, state, writes_cache=True, next_block=None):
         h = pending if isinstance(pending, ops.ScaledRows) else self.norm1.forward(resid, pending, step)
+        if self.feed_forward is None:
+            sink = next_block.entry_sink(resid, step) if self.mixer.fuses_norms(step) and next_block is not None else None
+            if sink is not None:
+                return resid, self.mixer.forward(h, step, cache, state, writes_cache, sink=sink)
+            return resid, self.mixer.forward(h, step, cache, state, writes_cache)
         mixer_fuses, ff_fuses = self.mixer.fuses_norms(step), self.feed_forward.fuses_norms(step)
         sink = self.norm2.sink(resid, step) if mixer_fuses and ff_fuses else None
         if sink is not None:

@@ -11,7 +11,7 @@ from .base import Mixer, Part, build_mixer, register_mixer
 
 class ParallelMixer(Mixer):
     """Every branch reads the mixer's input; the result is the mean of the branches' outputs, each first
-    RMS-normed over the model width with a weight of its own.  A call of the run order has one cache slot and
+    RMS-normed over the model width with a weight of its own (or, as the spec says, their weighted sum as they are).  A call of the run order has one cache slot and
     one state, so at most one branch keeps a paged cache and at most one a state; they get the call's.
 
     An arrangement that can take the sum into a kernel of its own asks `forward_branches` for the outputs with
@@ -20,8 +20,13 @@ class ParallelMixer(Mixer):
     def __init__(self, spec, dtype, device):
         self.spec = spec
         self.dtype = dtype
-        if not spec.branches or len(spec.branches) != len(spec.out_norms):
+        if not spec.branches or (spec.out_norms is not None and len(spec.branches) != len(spec.out_norms)):
             raise ValueError("a parallel mixer takes one output norm a branch")
+        coefficients = getattr(spec, "coefficients", None)
+        if coefficients is not None and len(coefficients) != len(spec.branches):
+            raise ValueError("a parallel mixer takes one coefficient a branch")
+        self.coefficients = [float(c) for c in coefficients] if coefficients is not None \
+            else [1.0 / len(spec.branches)] * len(spec.branches)
         self.branches = [build_mixer(b, dtype, device) for b in spec.branches]
         if sum(b.cache_spec() is not None for b in self.branches) > 1:
             raise ValueError("at most one branch of a parallel mixer keeps a paged cache")
@@ -32,13 +37,14 @@ class ParallelMixer(Mixer):
         self.graph_safe = all(getattr(b, "graph_safe", False) for b in self.branches)
 
     def tensors(self) -> dict:
-        out = {n: (self.spec.hidden,) for n in self.spec.out_norms}
+        out = {n: (self.spec.hidden,) for n in (self.spec.out_norms or ())}
         for b in self.branches:
             out.update(b.tensors())
         return out
 
     def load(self, src) -> None:
-        self.out_w = [src.get(n, "vector").contiguous() for n in self.spec.out_norms]
+        self.out_w = [src.get(n, "vector").contiguous() for n in self.spec.out_norms] \
+            if self.spec.out_norms is not None else [None] * len(self.branches)
         for b in self.branches:
             b.load(src)
 
@@ -61,9 +67,8 @@ class ParallelMixer(Mixer):
 
     def forward_branches(self, x, step, cache, state, writes_cache=True):
         """([(output, norm weight, coefficient), ...], eps of the norms): the terms of the result."""
-        c = 1.0 / len(self.branches)
         outs = []
-        for b, w in zip(self.branches, self.out_w):
+        for b, w, c in zip(self.branches, self.out_w, self.coefficients):
             y = b.forward(x, step, cache if b.cache_spec() is not None else None,
                           state if b.state_spec() is not None else None, writes_cache)
             outs.append((y, w, c))

@@ -38,6 +38,19 @@ def rope_inverse_frequencies(head_dim: int, theta: float, scaling=None) -> np.nd
     return out.astype(np.float32)
 
 
+def rope_inverse_frequencies_exact(head_dim: int, theta: float, scaling=None) -> np.ndarray:
+    """The same rule as `rope_inverse_frequencies`, worked out in float64 and rounded to float32 once."""
+    f = np.power(float(theta), -np.arange(0, head_dim, 2, dtype=np.float64) / float(head_dim))
+    if scaling is None or getattr(scaling, "rope_type", None) != "llama3":
+        return f.astype(np.float32)
+    factor, low, high = float(scaling.factor), float(scaling.low_freq_factor), float(scaling.high_freq_factor)
+    orig = float(scaling.original_max_position_embeddings)
+    wavelen = 2.0 * math.pi / f
+    smooth = (orig / wavelen - low) / (high - low) if high != low else np.zeros_like(f)
+    blended = (1.0 - smooth) * f / factor + smooth * f
+    return np.where(wavelen < orig / high, f, np.where(wavelen > orig / low, f / factor, blended)).astype(np.float32)
+
+
 def yarn_inverse_frequencies(dims: int, base: float, factor=None, original: float = 0.0, fast: float = 0.0,
                              slow: float = 0.0):
     """(float32 [dims / 2] frequencies, multiplier of cos and sin) of `YarnRopeSpec`'s rule, worked out
@@ -59,9 +72,14 @@ def yarn_inverse_frequencies(dims: int, base: float, factor=None, original: floa
 
 
 class Rope(PositionEncoding):
+    pairing = "half"         # entry i turns with entry i + head_dim / 2
+
     def __init__(self, spec, dtype, device):
+        if spec.head_dim <= 0 or spec.head_dim % 2:
+            raise ValueError(f"a rotation in pairs takes an even number of entries, got {spec.head_dim}")
         self.head_dim = spec.head_dim
-        inv = rope_inverse_frequencies(spec.head_dim, spec.theta, spec.scaling)
+        rule = rope_inverse_frequencies_exact if getattr(spec, "exact", False) else rope_inverse_frequencies
+        inv = rule(spec.head_dim, spec.theta, spec.scaling)
         self.inv_freq = torch.from_numpy(inv).to(device)
 
     def rotation(self):

@@ -27,8 +27,17 @@ class RoutedFF(FeedForward):
         self.shared = build_feed_forward(spec.shared, dtype, device) if spec.shared is not None else None
         if spec.shared_gate is not None and self.shared is None:
             raise ValueError("a gate on the shared expert, and no shared expert")
-        if spec.scoring not in ("sigmoid", "softmax_chosen"):
-            raise ValueError(f"experts are scored by 'sigmoid' or 'softmax_chosen', got {spec.scoring!r}")
+        if spec.scoring not in ("sigmoid", "softmax_chosen", "softmax"):
+            raise ValueError(f"experts are scored by 'sigmoid', 'softmax_chosen' or 'softmax', got {spec.scoring!r}")
+        self.n_identity = int(getattr(spec, "n_identity", 0) or 0)
+        self.groups = tuple(int(g) for g in spec.groups) if getattr(spec, "groups", None) is not None else None
+        n_out = spec.n_experts + self.n_identity
+        if self.groups is not None:
+            count, keep = self.groups
+            if count < 1 or n_out % count or not 1 <= keep <= count or spec.top > keep * (n_out // count):
+                raise ValueError(f"{n_out} router outputs do not form {count} equal groups of which {keep} hold {spec.top} choices")
+        if self.n_identity and spec.shared_gate is not None:
+            raise ValueError("the gate of a shared expert rides on the router's last row, where identity experts sit")
         self.router_bias = None
 
     def _names(self, pattern: str):
@@ -36,11 +45,12 @@ class RoutedFF(FeedForward):
 
     def tensors(self) -> dict:
         s = self.spec
-        out = {s.router: (s.n_experts, s.hidden)}
+        n_out = s.n_experts + self.n_identity
+        out = {s.router: (n_out, s.hidden)}
         if s.correction is not None:
-            out[s.correction] = (s.n_experts,)
+            out[s.correction] = (n_out,)
         if s.router_bias is not None:
-            out[s.router_bias] = (s.n_experts,)
+            out[s.router_bias] = (n_out,)
         for n in self._names(s.gate_proj) + self._names(s.up_proj):
             out[n] = (s.intermediate, s.hidden)
         for n in self._names(s.down_proj):
@@ -80,15 +90,16 @@ class RoutedFF(FeedForward):
         T = x.shape[0]
         with span("router"):
             plan = ops.moe_route(x, self.w_router, self.correction, s.n_experts, s.top, s.route_scale,
-                                 s.shared_gate is not None, step, router_bias=self.router_bias,
-                                 softmax_chosen=s.scoring == "softmax_chosen")
+                                 s.shared_gate is not None, step, router_bias=self.router_bias, scoring=s.scoring,
+                                 groups=self.groups, normalize=bool(getattr(s, "normalize", False)),
+                                 n_identity=self.n_identity)
         y_shared = self.shared.forward(x, step) if self.shared is not None else None
         with span("experts"):
             act = ops.moe_up(x, self.w_gate_up, plan, s.slope, self.limit, s.up_shift, step, self.interleave)
             y = ops.moe_down(act, self.w_down, plan, step)
         out = step.buffer("ffn_out", (T, s.hidden), self.dtype)
         with span("combine"):
-            return ops.moe_combine(y, plan, y_shared, out)
+            return ops.moe_combine(y, plan, y_shared, out, x=x)
 
 
 register_feed_forward("routed_ff", RoutedFF)

@@ -26,10 +26,15 @@ class RMSNormSpec:
 
 @dataclass(frozen=True)
 class RopeSpec:
-    """Rotate-half rotary encoding; `scaling` as in config.RopeScaling (llama3) or None."""
+    """Rotate-half rotary encoding; `scaling` as in config.RopeScaling (llama3) or None.  `head_dim` is the number
+    of entries that turn (entry i with entry i + head_dim / 2): a mixer that rotates itself may apply it to the
+    first entries of a longer head and let the rest pass."""
     head_dim: int
     theta: float
     scaling: Any = None
+    # True: the frequencies are worked out in float64 and rounded to float32 once (the default keeps the
+    # reference's float32 arithmetic, crates/model/src/rope.rs:19-49)
+    exact: bool = False
     kind: str = "rope"
 
 
@@ -103,7 +108,10 @@ class BiasedAttentionSpec:
     their norms.  `unit_norm`: queries and keys are divided by their root mean square per head without a weight
     (instead of `q_norm` / `k_norm`).  `q_temp` = (coef, every): queries are multiplied by 1 + coef ln(floor((p +
     1) / every) + 1) at position p.  `slopes`: one number a head, slope * distance is subtracted from a score.
-    `sink` (n_heads,): exp(sink_h) joins the denominator of head h's softmax, without a key or a value."""
+    `sink` (n_heads,): exp(sink_h) joins the denominator of head h's softmax, without a key or a value.
+    `rotation` may also be a rotate-half spec (`RopeSpec`, or a yarn spec with pairing "half").  `q_bias`, `k_bias`,
+    `v_bias`: biases of the three projections.  `out_gate` (n_heads * v_dim, hidden): every channel of every head's
+    output is multiplied by sigmoid of its row applied to the mixer's input (instead of `head_gate`)."""
     hidden: int
     n_heads: int
     n_kv_heads: int
@@ -127,6 +135,10 @@ class BiasedAttentionSpec:
     q_temp: Optional[tuple] = None   # (coef, every)
     slopes: Optional[tuple] = None   # one a head
     sink: Optional[str] = None       # (n_heads,)
+    q_bias: Optional[str] = None     # (n_heads * dim,)
+    k_bias: Optional[str] = None     # (n_kv_heads * dim,)
+    v_bias: Optional[str] = None     # (n_kv_heads * v_dim,)
+    out_gate: Optional[str] = None   # (n_heads * v_dim, hidden)
     kind: str = "biased_attention"
 
 
@@ -182,6 +194,52 @@ class LightningAttentionSpec:
 
 
 @dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with a fixed decay a head and no softmax or denominator: q, k = W h (n_heads x dim), rotated by
+    position where `rotation` (a rotate-half spec over the first entries of a head) is given, k times `k_scale`
+    (None: dim^(-1/2)); v = W_v h (n_heads x v_dim); S_t = decay_h S_(t-1) + k_t v_t^T (float32 state per request),
+    o_t = S_t^T q_t; each head's o is divided by its root mean square (times `out_norm` (v_dim,), None: no weight);
+    out = W_o (o * act(W_g h)) with `gate_act` "silu" or "sigmoid" (`gate_proj` None: no gate)."""
+    hidden: int
+    n_heads: int
+    dim: int
+    v_dim: int
+    decay: tuple                     # one factor a head
+    eps: float
+    q_proj: str                      # (n_heads * dim, hidden)
+    k_proj: str
+    v_proj: str                      # (n_heads * v_dim, hidden)
+    o_proj: str                      # (hidden, n_heads * v_dim)
+    gate_proj: Optional[str] = None  # (n_heads * v_dim, hidden)
+    gate_act: str = "silu"
+    out_norm: Optional[str] = None   # (v_dim,)
+    rotation: Any = None
+    k_scale: Optional[float] = None
+    kind: str = "retention"
+
+
+@dataclass(frozen=True)
+class ForgetGateRecurrenceSpec:
+    """Linear attention whose forget gate also decides what is written (HGRN2): q = silu(W_q h) (n_heads x dim), v =
+    W_v h (n_heads x v_dim), a forget gate per head and channel f = l + (1 - l) sigmoid(W_f h + f_bias) above the
+    lower bound l = `lower` (n_heads * dim,); S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T (float32 state per request),
+    o_t = S_t^T q_t; out = W_o (rmsnorm_per_head(o) * out_norm) with `out_norm` (v_dim,) shared by the heads."""
+    hidden: int
+    n_heads: int
+    dim: int
+    v_dim: int
+    eps: float
+    q_proj: str                      # (n_heads * dim, hidden)
+    f_proj: str                      # (n_heads * dim, hidden)
+    lower: str                       # (n_heads * dim,)
+    v_proj: str                      # (n_heads * v_dim, hidden)
+    o_proj: str                      # (hidden, n_heads * v_dim)
+    f_bias: Optional[str] = None     # (n_heads * dim,)
+    out_norm: Optional[str] = None   # (v_dim,)
+    kind: str = "forget_gate_recurrence"
+
+
+@dataclass(frozen=True)
 class GatedDeltaSpec:
     """The gated delta rule: q, k = W h (n_qk_heads x dim), v = W_v h (n_heads x v_dim); each passes a causal
     convolution over time per channel (`conv` taps, weights `<projection>.conv`-like tensors (channels, taps), the
@@ -217,11 +275,13 @@ class GatedDeltaSpec:
 class ParallelMixerSpec:
     """Several mixers side by side on the same input: the result is the mean of their outputs, each first
     RMS-normed over the model width with a weight of its own (`out_norms`, one tensor name a branch).  At most
-    one branch keeps a paged cache and at most one a per-request state."""
+    one branch keeps a paged cache and at most one a per-request state.  `out_norms` None: the outputs join as they
+    are.  `coefficients` (one number a branch; None: 1 / branches): the result is their weighted sum."""
     hidden: int
     branches: tuple                  # of mixer specs
-    out_norms: tuple                 # of tensor names, shape (hidden,)
+    out_norms: Optional[tuple]       # of tensor names, shape (hidden,)
     eps: float
+    coefficients: Optional[tuple] = None
     kind: str = "parallel"
 
 
@@ -242,7 +302,8 @@ class DenseFFSpec:
 @dataclass(frozen=True)
 class SwiGLUSpec:
     """W_down (g sigmoid(slope g) (u + up_shift)) with g = W_gate h and u = W_up h; with a `limit`, g is
-    cut at limit from above and u clipped to [-limit, limit] first.  The defaults are SwiGLU."""
+    cut at limit from above and u clipped to [-limit, limit] first.  The defaults are SwiGLU.  A `slope` of
+    +infinity is the limit max(g, 0) (u + up_shift): a unit gated by relu."""
     hidden: int
     intermediate: int
     gate_proj: str                   # (intermediate, hidden)
@@ -262,7 +323,14 @@ class RoutedFFSpec:
     `scoring` "softmax_chosen": the logits z = W_router h + router_bias choose, and the weights are the softmax
     over the chosen logits alone.
     Tensor names of expert e are the patterns with {e} filled in.  `shared`: a SwiGLUSpec that every token
-    runs through, added after multiplication by sigmoid(W_shared_gate h) where `shared_gate` is given."""
+    runs through, added after multiplication by sigmoid(W_shared_gate h) where `shared_gate` is given.
+
+    `scoring` "softmax": s = softmax(W_router h) over all router outputs.  `n_identity`: the router has that many
+    outputs more than there are experts (its last rows); they are scored, grouped and chosen like experts, and a
+    chosen one hands the token's input back (times its weight).  `groups` = (count, keep): the router outputs form
+    `count` equal groups of neighbours; a group ranks by its largest s + correction, and only outputs of the `keep`
+    best groups can be chosen.  `normalize`: the chosen scores are divided by their sum (+ 1e-20) before
+    route_scale."""
     hidden: int
     intermediate: int
     n_experts: int
@@ -280,6 +348,9 @@ class RoutedFFSpec:
     shared_gate: Optional[str] = None  # (1, hidden)
     router_bias: Optional[str] = None  # (n_experts,)
     scoring: str = "sigmoid"
+    n_identity: int = 0
+    groups: Optional[tuple] = None   # (count, keep)
+    normalize: bool = False
     kind: str = "routed_ff"
 
 
@@ -312,7 +383,8 @@ class LMHeadSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One block.  arrangement "prenorm": x += mixer(norm1(x)); x += feed_forward(norm2(x))
-    (crates/model/src/llama.rs:264-271).  arrangement "sandwich": each sublayer's result is normed
+    (crates/model/src/llama.rs:264-271; `feed_forward` None leaves the second line out, norm2 is then None too).
+    arrangement "sandwich": each sublayer's result is normed
     and scaled before it joins the stream, x += scale1 * post_norm1(mixer(norm1(x))) and the same
     with norm2, feed_forward, post_norm2, scale2; `feed_forward` None leaves the second sublayer out
     (norm2, post_norm2 and scale2 are then None too).  arrangement "outnorm": the sublayers read the

@@ -21,8 +21,8 @@ from .safetensors_io import save_file
 
 _STORE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 # kinds other than "matrix" and "norm": "offset" (weights stored around zero, biases), "gain" (free scalars),
-# "taps" (short convolutions over time)
-_STD = {"offset": 0.1, "gain": 1.0, "taps": 0.5}
+# "taps" (short convolutions over time), "fraction" (numbers between 0 and 1, around a half)
+_STD = {"offset": 0.1, "gain": 1.0, "taps": 0.5, "fraction": 0.15}
 
 
 def _tensor_key(seed: int, name: str) -> list[int]:
@@ -35,6 +35,8 @@ def random_tensor(seed: int, name: str, shape, kind: str, std: float = 0.02) -> 
     x = np.asarray(rng.standard_normal(size=tuple(shape), dtype=np.float32) * np.float32(_STD.get(kind, std)))
     if kind == "norm":
         x = x + np.float32(1.0)
+    if kind == "fraction":
+        x = np.clip(x + np.float32(0.5), np.float32(0.02), np.float32(0.98))
     return torch.from_numpy(np.array(x, dtype=np.float32).reshape(tuple(shape)))
 
 
@@ -60,6 +62,8 @@ def random_tensors_on_device(config_json: dict, seed: int, device, store_dtype: 
         x = torch.randn(tuple(shape), generator=gen, device=device, dtype=torch.float32) * _STD.get(kind, 0.02)
         if kind == "norm":
             x += 1.0
+        if kind == "fraction":
+            x = (x + 0.5).clamp_(0.02, 0.98)
         out[name] = x.to(_STORE[store_dtype])
     return out
 
