@@ -871,6 +871,184 @@ def workload_lanirax(args, torch, np) -> dict:
     return out
 
 
+def rumedra_config(width: int, vocab: int = 32000) -> dict:
+    """Four Rumedra layers at a real model's proportions.  Parallel layers: a window of 1,024 over heads of 64 in groups
+    of four with values as wide as keys, half of every head rotated, a gate a channel, beside retention with heads of
+    128 x 128.  Forget-gate layers: heads of 128 x 128.  Feed-forwards: relu-gated units of 8/3 widths, and routing to 4
+    of 32 router outputs (28 experts of half a width and 4 identity experts, in 4 groups of which 2 are kept) beside a
+    shared expert of half a width."""
+    H, R = width // 64, width // 128
+    rot = {"dims": 32, "base": 1000000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    left = {"heads": H, "kv_heads": max(1, H // 4), "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024}, "rot": rot}
+    right = {"heads": R, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, R - 1)) for h in range(R)],
+             "rot": {"dims": 128, "base": 1000000.0}}
+    par = {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.5}
+    rec = {"heads": R, "dim": 128, "vdim": 128}
+    moe = {"kind": "moe", "expert": {"ff": width // 2}, "shared": {"ff": width // 2},
+           "router": {"experts": 28, "identity": 4, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    dense = {"kind": "dense", "ff": width * 8 // 3 // 128 * 128}
+    return {"architecture": "Rumedra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 3.0},
+            "layers": [{"type": "parallel", "mixer": par, "mlp": dense}, {"type": "hgrn2", "mixer": rec, "mlp": moe},
+                       {"type": "parallel", "mixer": par, "mlp": moe}, {"type": "hgrn2", "mixer": rec, "mlp": dense}]}
+
+
+def rumedra_kernel_rooflines(width: int, B: int, ctx: int, T: int, pk: dict, torch, np) -> dict:
+    """The kernels that Rumedra adds or extends, alone, at the sizes of `rumedra_config(width)`, each beside the like
+    kernel of the closest models: {name: {"us", "ideal_us", "frac"}}.  Ideal: bytes that must move over the measured
+    copy bandwidth (single tokens, elementwise kernels), FLOPs over the measured bfloat16 GEMM rate (attention and
+    feed-forwards over prompts), or float32 FMAs over the FFMA rate of the SMs at their maximum clock (the recurrences
+    over prompts, float32 by design)."""
+    from rust_llm_inference_server_b200 import ops
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ffma = sms * 128 * 2 * pk.get("sm_max_mhz", 1965.0) * 1e6
+    page, nh, nkv, hd, window = 16, width // 64, max(1, width // 256), 64, 1024
+    rh, rd = width // 128, 128
+    E, ident, top, ff = 28, 4, 4, width // 2
+    bf, out = torch.bfloat16, {}
+    rnd = lambda *shape: torch.randn(*shape, device="cuda") * 0.3
+
+    def row(name, us, ideal_s):
+        out[name] = {"us": round(us, 1), "ideal_us": round(ideal_s * 1e6, 1), "frac": round(ideal_s * 1e6 / us, 3)}
+
+    sinks = rnd(nh).contiguous()
+    inv64, inv32 = torch.rand(64, device="cuda"), torch.rand(16, device="cuda")
+    for kind, reqs in (("decode", [(ctx - 1, 1)] * B), ("prefill", [(0, T)])):
+        st = _KernelStep(reqs, page, torch, np)
+        st.n_prefill_tokens = st.n_prefill_tokens if kind == "prefill" else 0
+        n = st.n_tokens
+        seen = B * min(ctx, window) if kind == "decode" else sum(min(i + 1, window) for i in range(T))
+        kc, vc, q = rnd(st.n_pages, nkv, page, hd).to(bf), rnd(st.n_pages, nkv, page, hd).to(bf), rnd(n, nh * hd).to(bf)
+        gate = rnd(n, nh * hd + 8).to(bf)[:, :nh * hd]
+        o = torch.empty_like(q)
+        attn = seen * nkv * hd * 2 * 2 / hbm if kind == "decode" else 2 * nh * seen * 2 * hd / tf
+        us = _graph_time_us(lambda: ops.attention_biased(q, kc, vc, o, None, gate, st, 0, nh, nkv, hd, hd, page, 0.125, window), torch)
+        row(f"window_gate_attention_{kind}", us, attn)
+        us = _graph_time_us(lambda: ops.attention_biased(q, kc, vc, o, None, None, st, 0, nh, nkv, hd, hd, page, 0.125, window,
+                                                         sinks=sinks), torch)
+        row(f"window_sink_attention_{kind}", us, attn)
+        # rotation by halves with biases and the paged write, beside the rotation of adjacent pairs with unit norms
+        N = (nh + 2 * nkv) * hd
+        proj, pb = rnd(n, N).to(bf), rnd(N).contiguous()
+        slots = torch.arange(n, device="cuda", dtype=torch.int32)
+        ones = torch.ones(hd, device="cuda")
+        moved = n * (N * 2 + (nh + 2 * nkv) * hd * 2) / hbm
+        us = _graph_time_us(lambda: ops.qk_norm_store(proj, 0, nh * hd, (nh + nkv) * hd, None, None, 1e-5, None, 0.0, q, kc, vc, slots,
+                                                      nh, nkv, hd, hd, page, rotation=(inv32, 32, 1.0), positions=st.positions,
+                                                      rot_half=True, proj_bias=pb), torch)
+        row(f"rotate_halves_bias_store_{kind}", us, moved)
+        us = _graph_time_us(lambda: ops.qk_norm_store(proj, 0, nh * hd, (nh + nkv) * hd, ones, ones, 1e-5, None, 0.0, q, kc, vc, slots,
+                                                      nh, nkv, hd, hd, page, rotation=(inv32, 32, 1.0), positions=st.positions), torch)
+        row(f"rotate_pairs_norm_store_{kind}", us, moved)
+        # the recurrences: inputs + walk, with a decay a head and a decay a channel, beside the decayed linear attention
+        # (silu inputs, one kernel or two) at the same head sizes
+        qk = rh * rd
+        proj3 = rnd(n, 3 * qk).to(bf)
+        state, decay = torch.zeros(len(reqs), rh, rd, rd, device="cuda"), torch.full((rh,), 0.97, device="cuda")
+        o3 = torch.empty(n, qk, device="cuda")
+        rows3, rows4 = torch.empty(n, 3 * qk, device="cuda"), torch.empty(n, 4 * qk, device="cuda")
+        lower, gb = torch.rand(qk, device="cuda"), rnd(qk).contiguous()
+        walk = B * rh * rd * rd * 4 * 2 / hbm if kind == "decode" else 2 * 2 * T * rh * rd * rd / ffma
+
+        def retention():
+            ops.recurrence_inputs(proj3, 0, qk, 2 * qk, rows3, rh, rd, rd, rotation=(inv64, 128), positions=st.positions,
+                                  k_scale=rd ** -0.5)
+            return ops.recurrence_scan(rows3, o3, state, decay, st, rh, rd, rd)
+
+        def forget_gate():
+            ops.recurrence_inputs(proj3, 0, qk, 2 * qk, rows4, rh, rd, rd, q_silu=True, lower=lower, gate_bias=gb)
+            return ops.recurrence_scan(rows4, o3, state, None, st, rh, rd, rd)
+        row(f"retention_{kind}", _graph_time_us(retention, torch), walk)
+        row(f"forget_gate_recurrence_{kind}", _graph_time_us(forget_gate, torch), walk)
+        us = _graph_time_us(lambda: ops.lightning_scan(proj3, 0, qk, 2 * qk, o3, state, decay, st, rh, rd, rd), torch)
+        row(f"decayed_linear_attention_{kind}", us, walk)
+        # routing by softmax in groups with identity experts (route + sort + both products + the weighted sum), beside
+        # routing by sigmoid scores over as many outputs that are all experts
+        x = rnd(n, width).to(bf)
+        y = torch.empty(n, width, dtype=bf, device="cuda")
+        for name, n_exp, n_id, kw in (("routed_ff_groups_identity", E, ident, dict(scoring="softmax", groups=(4, 2), normalize=True)),
+                                      ("routed_ff_sigmoid", E + ident, 0, {})):
+            wr, corr = rnd(n_exp + n_id, width).contiguous(), rnd(n_exp + n_id).contiguous()
+            wgu, wd = rnd(n_exp, 2 * ff, width).to(bf), rnd(n_exp, width, ff).to(bf)
+
+            def routed(wr=wr, corr=corr, wgu=wgu, wd=wd, n_exp=n_exp, n_id=n_id, kw=kw):
+                plan = ops.moe_route(x, wr, corr, n_exp, top, 2.5, False, st, n_identity=n_id, **kw)
+                act = ops.moe_up(x, wgu, plan, 1.0, float("inf"), 0.0, st, 4)
+                return ops.moe_combine(ops.moe_down(act, wd, plan, st), plan, None, y, x=x)
+            share = n_exp / (n_exp + n_id)              # of the pairs that reach an expert
+            flops = 2.0 * n * top * share * 3 * ff * width
+            row(f"{name}_{kind}", _graph_time_us(routed, torch),
+                min(n_exp, n * top) * 3 * ff * width * 2 / hbm if kind == "decode" else flops / tf)
+        # the unit gated by relu beside the unit gated by silu (gating in the first product's epilogue over prompts)
+        I = width * 8 // 3 // 128 * 128
+        wgu = torch.stack([rnd(I // 4, 4, width), rnd(I // 4, 4, width)], dim=1).reshape(2 * I, width).to(bf).contiguous()
+        wdn, act = rnd(width, I).to(bf), torch.empty(n, I, dtype=bf, device="cuda")
+
+        def relu_unit():
+            if n >= 128:
+                return ops.linear(ops.gemm_tcgen05(x, wgu, "glu4", glu=(float("inf"), None, 0.0)), wdn)
+            return ops.linear(ops.glu_act(ops.linear(x, wgu), act, float("inf"), None, 0.0, 4), wdn)
+
+        def silu_unit():
+            if n <= ops.STREAM_GEMM_ROWS:
+                return ops.linear(ops.stream_gemm(x, wgu, swiglu4=True), wdn)
+            return ops.linear(ops.gemm_tcgen05(x, wgu, "swiglu4"), wdn)
+        ideal = 3 * I * width * 2 / hbm if kind == "decode" else 2.0 * n * 3 * I * width / tf
+        row(f"relu_gated_ff_{kind}", _graph_time_us(relu_unit, torch), ideal)
+        row(f"silu_gated_ff_{kind}", _graph_time_us(silu_unit, torch), ideal)
+    return out
+
+
+def workload_rumedra(args, torch, np) -> dict:
+    """Prefill (one 2,048-token prompt) and decode (batch 8, context 4,096) of four Rumedra layers at two widths beside
+    four Lanirax layers (the closest model: a parallel mixer of window attention and a recurrence, routed feed-forwards)
+    and four Llama layers of the same width, random bfloat16 weights; then the stages of one step by CUDA-event spans
+    (eager launches), and the kernels alone, replayed from CUDA graphs, against their rooflines."""
+    from rust_llm_inference_server_b200 import LLM
+    from rust_llm_inference_server_b200.ops import profile
+    pk, pk_src = peaks()
+    B, ctx, page, T = args.batch, args.context, 16, PREFILL_TOKENS
+    steps = min(args.steps, 64)
+    out = {"workload": "rumedra", "metric": "prefill and decode tokens/s of four layers, Rumedra beside Lanirax and Llama at equal width",
+           "unit": "tokens/s", "impl": "ours", "dtype": "bf16", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+           "data": "synthetic: uniform-random token ids, random-init weights (device generator)",
+           "config": {"global_batch": B, "seq_len": ctx, "prefill_tokens": T, "page_size": page, "layers": 4},
+           "peaks": dict(pk, source=pk_src), "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for width in (1024, 2048):
+        row = {}
+        for name, cfg in (("rumedra", rumedra_config(width)), ("lanirax", lanirax_config(width)), ("llama", llama_config_like(width))):
+            llm = LLM.from_random(cfg, 8, dtype="bfloat16", on_device=True, max_seq_len=ctx + page,
+                                  num_blocks=B * (ctx + page) // page + 64, block_size=page, max_num_seqs=B,
+                                  max_batched_tokens=max(2048, B), prefix_caching=False)
+            pre = prefill_run(llm, T, 5, 3, torch, np)
+            ms, launches = decode_run(llm, B, steps, args.warmup, ctx, torch)
+            profile.enable(True)
+            prefill_run(llm, T, 3, 2, torch, np)
+            profile.take_report()
+            prefill_run(llm, T, 3, 0, torch, np)
+            pre_stages = {k: round(v[0] / 3 * 1e3, 1) for k, v in profile.take_report().items()}
+            decode_run(llm, B, 8, 4, ctx, torch, fill=False)
+            dec_stages = {k: round(v[0] / 8 * 1e3, 1) for k, v in profile.take_report().items()}
+            profile.enable(False)
+            row[name] = {"prefill_tokens_per_s": round(T / (pre / 1e3), 1), "prefill_ms": round(pre, 3),
+                         "decode_tokens_per_s": round(B / (ms / 1e3), 1), "decode_ms_per_step": round(ms, 4),
+                         "launches_per_decode_step": launches,
+                         "weight_bytes": int(sum(p.numel() * p.element_size() for p in _model_tensors(llm.model))),
+                         "prefill_stage_us": pre_stages, "decode_stage_us": dec_stages}
+            del llm
+            torch.cuda.empty_cache()
+        row["rooflines"] = rumedra_kernel_rooflines(width, B, ctx, T, pk, torch, np)
+        out["sizes"][f"width{width}"] = row
+    out["clocks"] = clocks.stop()
+    head = out["sizes"]["width2048"]["rumedra"]
+    out["value"] = head["decode_tokens_per_s"]
+    out["ms_per_step"] = head["decode_ms_per_step"]
+    out["gpu_launches"] = int(round(head["launches_per_decode_step"] * steps))
+    return out
+
+
 def _model_tensors(model):
     seen = {}
     for part in model.parts():
@@ -901,7 +1079,7 @@ def print_timeline(records: list) -> None:
 
 
 WORKLOADS = {"3b": workload_3b, "8b": workload_8b, "1b-fp32": workload_1b_fp32, "lasapel": workload_lasapel,
-             "gavodra": workload_gavodra, "lanirax": workload_lanirax}
+             "gavodra": workload_gavodra, "lanirax": workload_lanirax, "rumedra": workload_rumedra}
 
 
 def main() -> int:

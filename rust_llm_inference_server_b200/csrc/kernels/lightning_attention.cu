@@ -236,8 +236,12 @@ template <typename T>
 __global__ __launch_bounds__(256) void recurrence_inputs_kernel(
     const T* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, float* __restrict__ out, int nh, int d,
     int dv, const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ positions, float k_scale,
-    int q_silu, const float* __restrict__ lower, const float* __restrict__ gate_bias) {
-    pdl_wait_and_trigger();
+    int q_silu, const float* __restrict__ lower, const float* __restrict__ gate_bias, int late_trigger) {
+    // Over prompts the walk that follows has few CTAs and wants one to an SM: let in early, while this grid still fills
+    // the SMs, its CTAs would land several to an SM wherever room appears first (the walk then runs three times as
+    // long).  So in long steps it is let in at the end.
+    pdl_wait();
+    if (!late_trigger) pdl_trigger();
     const int t = blockIdx.x;
     const int qk = nh * d, hv = nh * dv;
     const int width = 2 * qk + hv + (lower != nullptr ? qk : 0);
@@ -273,6 +277,7 @@ __global__ __launch_bounds__(256) void recurrence_inputs_kernel(
         if (is_q && q_silu) val = silu_f(val);
         orow[c] = is_q ? val : val * k_scale;
     }
+    if (late_trigger) pdl_trigger();
 }
 }  // namespace
 
@@ -288,12 +293,13 @@ extern "C" int rlis_recurrence_inputs(const void* proj, long long stride, int q_
         return RLIS_ERR_UNSUPPORTED;
     const int cols = 2 * nh * d + nh * dv;
     const dim3 blocks(n_tokens, (cols + 1023) / 1024 < 8 ? (cols + 1023) / 1024 : 8);
+    const int late = n_tokens >= 64 ? 1 : 0;
     if (dtype == RLIS_F32)
         rlis_launch(recurrence_inputs_kernel<float>, blocks, 256, 0, stream, (const float*)proj, stride, q_off, k_off, v_off,
-                    out, nh, d, dv, inv_freq, rot_dims, positions, k_scale, q_silu, lower, gate_bias);
+                    out, nh, d, dv, inv_freq, rot_dims, positions, k_scale, q_silu, lower, gate_bias, late);
     else if (dtype == RLIS_BF16)
         rlis_launch(recurrence_inputs_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)proj, stride, q_off, k_off, v_off,
-                    out, nh, d, dv, inv_freq, rot_dims, positions, k_scale, q_silu, lower, gate_bias);
+                    out, nh, d, dv, inv_freq, rot_dims, positions, k_scale, q_silu, lower, gate_bias, late);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();
