@@ -951,11 +951,16 @@ def rumedra_kernel_rooflines(width: int, B: int, ctx: int, T: int, pk: dict, tor
         walk = B * rh * rd * rd * 4 * 2 / hbm if kind == "decode" else 2 * 2 * T * rh * rd * rd / ffma
 
         def retention():
+            if n < ops.RECURRENCE_INPUT_PASS_TOKENS:
+                return ops.recurrence_scan_rows(proj3, 0, qk, 2 * qk, o3, state, decay, st, rh, rd, rd, rotation=(inv64, 128),
+                                                k_scale=rd ** -0.5)
             ops.recurrence_inputs(proj3, 0, qk, 2 * qk, rows3, rh, rd, rd, rotation=(inv64, 128), positions=st.positions,
                                   k_scale=rd ** -0.5)
             return ops.recurrence_scan(rows3, o3, state, decay, st, rh, rd, rd)
 
         def forget_gate():
+            if n < ops.RECURRENCE_INPUT_PASS_TOKENS:
+                return ops.recurrence_scan_rows(proj3, 0, qk, 2 * qk, o3, state, None, st, rh, rd, rd, lower=lower, gate_bias=gb)
             ops.recurrence_inputs(proj3, 0, qk, 2 * qk, rows4, rh, rd, rd, q_silu=True, lower=lower, gate_bias=gb)
             return ops.recurrence_scan(rows4, o3, state, None, st, rh, rd, rd)
         row(f"retention_{kind}", _graph_time_us(retention, torch), walk)
@@ -985,9 +990,9 @@ def rumedra_kernel_rooflines(width: int, B: int, ctx: int, T: int, pk: dict, tor
         wdn, act = rnd(width, I).to(bf), torch.empty(n, I, dtype=bf, device="cuda")
 
         def relu_unit():
-            if n >= 128:
-                return ops.linear(ops.gemm_tcgen05(x, wgu, "glu4", glu=(float("inf"), None, 0.0)), wdn)
-            return ops.linear(ops.glu_act(ops.linear(x, wgu), act, float("inf"), None, 0.0, 4), wdn)
+            if n <= ops.STREAM_GEMM_ROWS:
+                return ops.linear(ops.stream_gemm(x, wgu, swiglu4=True, slope=float("inf")), wdn)
+            return ops.linear(ops.gemm_tcgen05(x, wgu, "glu4", glu=(float("inf"), None, 0.0)), wdn)
 
         def silu_unit():
             if n <= ops.STREAM_GEMM_ROWS:

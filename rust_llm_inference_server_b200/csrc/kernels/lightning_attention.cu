@@ -26,14 +26,25 @@ constexpr int THREADS = COLS * SLICES;
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
+// What the walk needs to make its inputs itself in short steps (PREP 1: rotation by halves and a scale on k; PREP 2: silu
+// of q and the forget gate); the arithmetic is that of recurrence_inputs_kernel below.
+struct PrepArgs {
+    const float* inv_freq;
+    int rot_dims;
+    float k_scale;
+    const float* lower;
+    const float* gate_bias;
+};
+
 // E = entries of a column that one thread holds: ceil(d / 8), rounded up to a multiple of 4 so that a
 // thread reads its share of k and q from shared memory in 16-byte vectors.  Thread `slice` owns the
 // entries slice * E .. slice * E + E - 1 (those at or beyond d stay zero).
-template <typename T, int E, bool SILU, bool VEC>
+template <typename T, int E, bool SILU, bool VEC, int PREP = 0>
 __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     const T* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, float* __restrict__ out,
     float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ cu_seqlens,
-    const int* __restrict__ ctx_lens, const int* __restrict__ state_slots, int nh, int d, int dv, int a_off) {
+    const int* __restrict__ ctx_lens, const int* __restrict__ state_slots, int nh, int d, int dv, int a_off,
+    const PrepArgs pa) {
     pdl_wait();     // (the next kernel is let in at the end: this one runs long on few warps)
     // tokens staged at a time (shared memory holds them; a third array with a decay a channel)
     constexpr int TOK = VEC ? (E > 16 ? 4 : 8) : (E > 8 ? 8 : 16);
@@ -72,7 +83,10 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     }
     // what one thread stages of q and k: element idx = threadIdx.x + j * THREADS of the [TOK][DP] tile
     constexpr int PER = TOK * DP / THREADS;
-    float rq[PER], rk[PER], ra[VEC ? PER : 1], rv[(TOK * COLS + THREADS - 1) / THREADS];
+    float rq[PER], rk[PER], ra[VEC && PREP != 2 ? PER : 1], rv[(TOK * COLS + THREADS - 1) / THREADS];
+    float rqp[PREP == 1 ? PER : 1], rkp[PREP == 1 ? PER : 1];      // the entries that q and k turn with
+    const int half = pa.rot_dims >> 1;
+    const int pos0 = ctx_lens[b] - n;                              // position of the request's first token of this step
     auto fetch = [&](int t0) {                     // raw values of the next tokens, into registers
         const int nt = min(TOK, n - t0);
 #pragma unroll
@@ -82,7 +96,13 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
             const T* r = proj + (size_t)(row0 + t0 + (ok ? tt : 0)) * stride + h * d + (ok ? i : 0);
             rq[j] = ok ? to_f<T>(r[q_off]) : 0.f;
             rk[j] = ok ? to_f<T>(r[k_off]) : 0.f;
-            if (VEC) ra[j] = ok ? to_f<T>(r[a_off]) : 0.f;
+            if (VEC && PREP != 2) ra[j] = ok ? to_f<T>(r[a_off]) : 0.f;
+            if (PREP == 1) {
+                const bool turns = ok && i < pa.rot_dims;
+                const int pi = i < half ? half : -half;
+                rqp[j] = turns ? to_f<T>(r[q_off + pi]) : 0.f;
+                rkp[j] = turns ? to_f<T>(r[k_off + pi]) : 0.f;
+            }
         }
 #pragma unroll
         for (int j = 0; j < (TOK * COLS + THREADS - 1) / THREADS; ++j) {
@@ -99,9 +119,32 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
         for (int j = 0; j < PER; ++j) {
             const int idx = threadIdx.x + j * THREADS, tt = idx / DP, i = idx - tt * DP;
             const int at = tt * DPS + (i / E) * ES + i % E;
-            qs[at] = SILU ? silu_f(rq[j]) : rq[j];  // silu(0) = 0 keeps the padding zero
-            ks[at] = SILU ? silu_f(rk[j]) : rk[j];
-            if (VEC) as[at] = ra[j];
+            if (PREP == 1) {
+                float qv = rq[j], kv = rk[j];
+                if (tt < nt && i < pa.rot_dims) {          // (a stage's empty places are zeros and stay so)
+                    float sn, cs;
+                    sincosf((float)(pos0 + t0 + tt) * pa.inv_freq[i < half ? i : i - half], &sn, &cs);
+                    qv = i < half ? rope_first(qv, rqp[j], cs, sn) : rope_second(rqp[j], qv, cs, sn);
+                    kv = i < half ? rope_first(kv, rkp[j], cs, sn) : rope_second(rkp[j], kv, cs, sn);
+                }
+                qs[at] = qv;
+                ks[at] = kv * pa.k_scale;
+            } else if (PREP == 2) {
+                const bool ok = tt < nt && i < d;
+                float a = 0.f;
+                if (ok) {
+                    const float l = pa.lower[h * d + i];
+                    const float z = rk[j] + (pa.gate_bias != nullptr ? pa.gate_bias[h * d + i] : 0.f);
+                    a = l + (1.0f - l) * (1.0f / (1.0f + expf(-z)));
+                }
+                qs[at] = silu_f(rq[j]);
+                ks[at] = ok ? 1.0f - a : 0.f;
+                as[at] = a;
+            } else {
+                qs[at] = SILU ? silu_f(rq[j]) : rq[j];  // silu(0) = 0 keeps the padding zero
+                ks[at] = SILU ? silu_f(rk[j]) : rk[j];
+                if (VEC) as[at] = ra[j];
+            }
         }
 #pragma unroll
         for (int j = 0; j < (TOK * COLS + THREADS - 1) / THREADS; ++j) {
@@ -176,13 +219,13 @@ __global__ void silu_rows_kernel(const T* __restrict__ x, long long stride, floa
     pdl_trigger();
 }
 
-template <typename T, bool SILU, bool VEC = false>
+template <typename T, bool SILU, bool VEC = false, int PREP = 0>
 int launch_scan(const T* proj, long long stride, int q_off, int k_off, int v_off, float* out, float* state,
                 const float* decay, const int* cu, const int* ctx, const int* slots, dim3 grid, int nh, int d, int dv,
-                cudaStream_t stream, int a_off = 0) {
+                cudaStream_t stream, int a_off = 0, PrepArgs pa = PrepArgs{}) {
     const int e = (d + SLICES - 1) / SLICES;
-#define RLIS_SCAN(E) rlis_launch(lightning_scan_kernel<T, E, SILU, VEC>, grid, THREADS, 0, stream, proj, stride, q_off, k_off, \
-                                 v_off, out, state, decay, cu, ctx, slots, nh, d, dv, a_off)
+#define RLIS_SCAN(E) rlis_launch(lightning_scan_kernel<T, E, SILU, VEC, PREP>, grid, THREADS, 0, stream, proj, stride, q_off, k_off, \
+                                 v_off, out, state, decay, cu, ctx, slots, nh, d, dv, a_off, pa)
     if (e <= 4) RLIS_SCAN(4);
     else if (e <= 8) RLIS_SCAN(8);
     else if (e <= 16) RLIS_SCAN(16);
@@ -320,4 +363,31 @@ extern "C" int rlis_recurrence_scan(const float* rows, long long width, int q_of
                                                 state_slots, grid, nh, d, dv, stream);
     return launch_scan<float, false, true>(rows, width, q_off, k_off, v_off, out, state, nullptr, cu_seqlens, ctx_lens,
                                            state_slots, grid, nh, d, dv, stream, a_off);
+}
+
+// The same walk straight from the projection's rows, its inputs made while the tokens are staged (short steps: every CTA
+// of a head makes them again, which a prompt's portion would pay dv / 16 times): rotation of q and k by halves and the
+// scale on k with a decay a head (`decay` given), or silu of q and the forget gate with a decay a channel (`lower` given).
+extern "C" int rlis_recurrence_scan_rows(const void* proj, long long stride, int q_off, int k_off, int v_off, float* out,
+                                         float* state, const float* decay, const int* cu_seqlens, const int* ctx_lens,
+                                         const int* state_slots, int n_seqs, int nh, int d, int dv, const float* inv_freq,
+                                         int rot_dims, float k_scale, const float* lower, const float* gate_bias, int dtype,
+                                         cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (d <= 0 || d > SLICES * MAX_E || dv <= 0 || nh <= 0 || nh > 65535 || (decay == nullptr) == (lower == nullptr))
+        return RLIS_ERR_UNSUPPORTED;
+    if (rot_dims < 0 || rot_dims > d || (rot_dims & 1) || (rot_dims > 0 && (inv_freq == nullptr || lower != nullptr)))
+        return RLIS_ERR_UNSUPPORTED;
+    dim3 grid(n_seqs, nh, (dv + COLS - 1) / COLS);
+    if (grid.z > 65535) return RLIS_ERR_UNSUPPORTED;
+    const PrepArgs pa{inv_freq, rot_dims, k_scale, lower, gate_bias};
+#define RLIS_ROWS(T) (decay != nullptr                                                                                         \
+        ? launch_scan<T, false, false, 1>((const T*)proj, stride, q_off, k_off, v_off, out, state, decay, cu_seqlens, ctx_lens,   \
+                                          state_slots, grid, nh, d, dv, stream, 0, pa)                                            \
+        : launch_scan<T, false, true, 2>((const T*)proj, stride, q_off, k_off, v_off, out, state, nullptr, cu_seqlens, ctx_lens,  \
+                                         state_slots, grid, nh, d, dv, stream, 0, pa))
+    if (dtype == RLIS_F32) return RLIS_ROWS(float);
+    if (dtype == RLIS_BF16) return RLIS_ROWS(bf16);
+#undef RLIS_ROWS
+    return RLIS_ERR_UNSUPPORTED;
 }

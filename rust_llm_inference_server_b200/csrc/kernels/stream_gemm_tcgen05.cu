@@ -131,6 +131,7 @@ struct NormFuse {
     const float* norm_w;        // sink: [N] weight of the norm that follows
     bf16* xn;                   // sink: [M, N] = bf16(resid * norm_w)
     float* out_partials;        // sink: [tiles, M]
+    float gate_slope;           // gated epilogue: g sigmoid(slope g) * u (1: silu; +inf: max(g, 0))
 };
 
 // A float into the shared memory of the cluster's CTA `rank` (at the offset of `local`), counted
@@ -157,12 +158,12 @@ constexpr int CHUNK_F = 8;                   // features of a chunk
 constexpr int N_CHUNKS = SF / CHUNK_F;       // 16 chunks a tile
 
 template <int EPI, typename OutT>
-__device__ __forceinline__ void store_token(OutT* __restrict__ y, float v, int t, int f, int lane, int N) {
+__device__ __forceinline__ void store_token(OutT* __restrict__ y, float v, int t, int f, int lane, int N, float slope) {
     if (EPI == 1) {
         // lanes 8i..8i+3 hold gate, 8i+4..8i+7 the matching up values
         const float other = __shfl_xor_sync(0xffffffffu, v, 4);
         if ((lane & 4) == 0 && f + 4 < N)
-            y[(size_t)t * (N >> 1) + ((f >> 3) << 2) + (f & 3)] = from_f<OutT>(v / (1.0f + expf(-v)) * other);
+            y[(size_t)t * (N >> 1) + ((f >> 3) << 2) + (f & 3)] = from_f<OutT>(glu_gate(v, slope) * other);
     } else if (f < N) {
         y[(size_t)t * N + f] = from_f<OutT>(v);
     }
@@ -337,7 +338,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
             for (int j = 0; j < 16; ++j)
                 if (c * 16 + j < M)
                     store_token<EPI, OutT>(y, __uint_as_float(r[j]) * (scaled ? ctrl->rstd[c * 16 + j] : 1.0f),
-                                           c * 16 + j, f, lane, N);
+                                           c * 16 + j, f, lane, N, nf.gate_slope);
         }
     } else {
         // Once every CTA of the cluster is done with its products, the stages are free everywhere:
@@ -388,7 +389,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
                         const float g = v * sc;
                         const float other = __shfl_xor_sync(0xffffffffu, g, 4);
                         if (ok && t < M && (fi & 4) == 0 && fo + 4 < N)
-                            y[(size_t)t * (N >> 1) + ((fo >> 3) << 2) + (fo & 3)] = from_f<OutT>(g / (1.0f + expf(-g)) * other);
+                            y[(size_t)t * (N >> 1) + ((fo >> 3) << 2) + (fo & 3)] = from_f<OutT>(glu_gate(g, nf.gate_slope) * other);
                     } else if (ok && t < M && fo < N) {
                         y[(size_t)t * N + fo] = from_f<OutT>(v * sc);
                     }
@@ -426,7 +427,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
                     const float r_old = slot == 0 ? sink_r0 : (good && f < N ? nf.resid[(size_t)t * N + f] : 0.f);
                     sink_token(nf, ctrl->red, v, t, f, tile, M, N, good, r_old, sink_w);
                 } else if (good) {
-                    store_token<EPI, OutT>(y, v * (scaled ? ctrl->rstd[t] : 1.0f), t, f, lane, N);
+                    store_token<EPI, OutT>(y, v * (scaled ? ctrl->rstd[t] : 1.0f), t, f, lane, N, nf.gate_slope);
                 }
             }
         }
@@ -539,8 +540,8 @@ extern "C" int* rlis_stream_gemm_error_addr(void) { return tc::error_word_addr()
 extern "C" void rlis_stream_gemm_set_target(int ctas) { g_target_ctas = ctas; }
 extern "C" void rlis_stream_gemm_set_min_stages(int n) { g_min_stages = n; }
 
-// out_dtype: RLIS_BF16 or RLIS_F32.  epilogue 0: y [M, N]; 1 (SwiGLU, rows of W interleaved
-// gate/up in blocks of 4, N a multiple of 8): y [M, N / 2].  M up to 128; K a multiple of 8;
+// out_dtype: RLIS_BF16 or RLIS_F32.  epilogue 0: y [M, N]; 1 (gated unit, rows of W interleaved
+// gate/up in blocks of 4, N a multiple of 8): y [M, N / 2] = g sigmoid(gate_slope g) u (slope 1: SwiGLU; +inf: relu).  M up to 128; K a multiple of 8;
 // x and W 16-byte aligned.
 //
 // Scaled rows (epilogues 0 and 1; in_partials not null): x is bf16(resid * norm weight) and
@@ -551,13 +552,14 @@ extern "C" void rlis_stream_gemm_set_min_stages(int n) { g_min_stages = n; }
 extern "C" int rlis_stream_gemm_fused(const void* x, const void* W, void* y, int M, int N, int K, int out_dtype,
                                       int epilogue, const float* in_partials, int n_partials, int norm_dim, float eps,
                                       float* resid, const float* norm_w, void* xn, float* out_partials,
-                                      cudaStream_t stream) {
+                                      float gate_slope, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 128 || K <= 0 || (K & 7) != 0) return RLIS_ERR_UNSUPPORTED;
     if (epilogue == 1 && (N & 7) != 0) return RLIS_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(W) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
         return RLIS_ERR_UNSUPPORTED;
     NormFuse nf{};
+    nf.gate_slope = gate_slope;
     if (in_partials != nullptr) {
         if (epilogue == 2 || n_partials <= 0 || norm_dim <= 0) return RLIS_ERR_UNSUPPORTED;
         nf.in_partials = in_partials;
@@ -581,8 +583,8 @@ extern "C" int rlis_stream_gemm_fused(const void* x, const void* W, void* y, int
 }
 
 extern "C" int rlis_stream_gemm_bf16(const void* x, const void* W, void* y, int M, int N, int K,
-                                     int out_dtype, int epilogue, cudaStream_t stream) {
+                                     int out_dtype, int epilogue, float gate_slope, cudaStream_t stream) {
     if (epilogue == 2) return RLIS_ERR_UNSUPPORTED;
     return rlis_stream_gemm_fused(x, W, y, M, N, K, out_dtype, epilogue, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr,
-                                  nullptr, stream);
+                                  nullptr, gate_slope, stream);
 }

@@ -652,6 +652,44 @@ def recurrence_scan(rows: torch.Tensor, out: torch.Tensor, state: torch.Tensor, 
     return out
 
 
+RECURRENCE_INPUT_PASS_TOKENS = 64   # steps of this many tokens and more make the recurrence's inputs in a pass of their own
+
+
+def recurrence_scan_rows(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor, state: torch.Tensor,
+                         decay: torch.Tensor | None, step, n_heads: int, d: int, dv: int, rotation: tuple | None = None,
+                         k_scale: float = 1.0, lower: torch.Tensor | None = None,
+                         gate_bias: torch.Tensor | None = None) -> torch.Tensor:
+    """`recurrence_inputs` and `recurrence_scan` in one kernel, for short steps: the walk makes its inputs from the
+    projection's rows while it stages them.  With `decay` (float32 [n_heads]): q and k rotated by halves at the tokens'
+    positions (`rotation` = (frequencies, r)), k times `k_scale`.  With `lower` (and no `decay`): q = silu(q), the forget
+    gate a = lower + (1 - lower) sigmoid(z + gate_bias) from the columns at k_off is the decay a channel and k = 1 - a."""
+    T, N = proj.shape
+    qk, hv = n_heads * d, n_heads * dv
+    _req(proj, "proj")
+    _req(out, "out", torch.float32, (T, hv))
+    _req(state, "state", torch.float32, (None, n_heads, dv, d))
+    if (decay is None) == (lower is None):
+        raise KernelError("recurrence_scan_rows: a decay a head, or the lower bounds of a forget gate")
+    if max(q_off, k_off) + qk > N or v_off + hv > N:
+        raise KernelError("recurrence_scan_rows: the column offsets reach beyond the projection's rows")
+    inv_freq, rot_dims = rotation if rotation is not None else (None, 0)
+    if rot_dims:
+        _req(inv_freq, "rotation frequencies", torch.float32, (rot_dims // 2,))
+        if rot_dims % 2 or rot_dims > d or lower is not None:
+            raise KernelError(f"recurrence_scan_rows: {rot_dims} rotated entries do not fit plain heads of {d} in pairs")
+    for v, nm, n in ((decay, "decay", n_heads), (lower, "lower", qk), (gate_bias, "gate_bias", qk)):
+        if v is not None:
+            _req(v, nm, torch.float32, (n,))
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    check(lib().rlis_recurrence_scan_rows(proj.data_ptr(), proj.stride(0), int(q_off), int(k_off), int(v_off), out.data_ptr(),
+                                          state.data_ptr(), ptr(decay), step.cu_seqlens.data_ptr(), step.ctx_lens.data_ptr(),
+                                          step.state_slots.data_ptr(), step.n_seqs, n_heads, d, dv,
+                                          inv_freq.data_ptr() if rot_dims else None, int(rot_dims), float(k_scale), ptr(lower),
+                                          ptr(gate_bias), _code(proj.dtype), _stream()), "recurrence_scan_rows")
+    _count("recurrence_scan_rows" + (".channel_decay" if decay is None else ""))
+    return out
+
+
 FUSE_NORMS = True          # debug switch "fuse_norms": 0 runs every norm as a kernel
 STREAM_MAX_ROWS = 128     # what the weight-streaming kernel takes
 DECODE_GEMM_ROWS = 16     # up to this many rows its sink epilogue works: the norms go into the products
@@ -685,11 +723,12 @@ class ResidualSink:
         self.resid, self.weight, self.eps = resid, weight, float(eps)
 
 
-def stream_gemm(x, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = False, sink: ResidualSink | None = None):
+def stream_gemm(x, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = False, sink: ResidualSink | None = None,
+                slope: float = 1.0):
     """y = x @ w^T for at most 128 rows of bfloat16 x: the decode step's weight-streaming product on
     the tcgen05 tensor cores (TMA-fed, weights as the M side, k split over CTAs).  `swiglu4`: w is a
-    gate|up matrix interleaved in blocks of 4 rows and the result is silu(gate) * up, [M, N / 2].
-    `x` may be ScaledRows: the rows' scale is applied to the result.  `sink` (up to 16 rows): the
+    gate|up matrix interleaved in blocks of 4 rows and the result is silu(gate) * up, [M, N / 2]; with a `slope`,
+    gate sigmoid(slope gate) * up (+inf: max(gate, 0) * up).  `x` may be ScaledRows: the rows' scale is applied to the result.  `sink` (up to 16 rows): the
     result, rounded to bfloat16, is added to sink.resid in place and the ScaledRows of the norm that
     follows are returned instead of y."""
     scaled = x if isinstance(x, ScaledRows) else None
@@ -704,7 +743,7 @@ def stream_gemm(x, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = Fa
     if scaled is None and sink is None:
         out = torch.empty((M, N // 2 if swiglu4 else N), dtype=out_dtype, device=x.device)
         check(lib().rlis_stream_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _code(out_dtype),
-                                          1 if swiglu4 else 0, _stream()), "stream_gemm")
+                                          1 if swiglu4 else 0, float(slope), _stream()), "stream_gemm")
         _count("stream_gemm.swiglu" if swiglu4 else "stream_gemm")
         return out
     in_p, n_p, dim, eps = 0, 0, 0, 0.0
@@ -719,7 +758,7 @@ def stream_gemm(x, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = Fa
     if sink is None:
         out = torch.empty((M, N // 2 if swiglu4 else N), dtype=out_dtype, device=x.device)
         check(lib().rlis_stream_gemm_fused(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _code(out_dtype),
-                                           1 if swiglu4 else 0, in_p, n_p, dim, eps, 0, 0, 0, 0, _stream()),
+                                           1 if swiglu4 else 0, in_p, n_p, dim, eps, 0, 0, 0, 0, float(slope), _stream()),
               "stream_gemm")
         _count("stream_gemm.scaled.swiglu" if swiglu4 else "stream_gemm.scaled")
         return out
@@ -731,7 +770,7 @@ def stream_gemm(x, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = Fa
     partials = torch.empty(((N + 127) // 128, M), dtype=torch.float32, device=x.device)
     check(lib().rlis_stream_gemm_fused(x.data_ptr(), w.data_ptr(), 0, M, N, K, _code(torch.bfloat16), 2, 0, 0, 0, 0.0,
                                        sink.resid.data_ptr(), sink.weight.data_ptr(), xn.data_ptr(),
-                                       partials.data_ptr(), _stream()), "stream_gemm")
+                                       partials.data_ptr(), 1.0, _stream()), "stream_gemm")
     _count("stream_gemm.sink")
     return ScaledRows(xn, partials, N, sink.eps)
 

@@ -44,6 +44,7 @@ SIGNATURES = {
     "rlis_attention_latent_decode": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_lightning_scan": [P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P, I, P],
     "rlis_recurrence_inputs": [P, LL, I, I, I, P, I, I, I, I, P, I, P, F, I, P, P, I, P],
+    "rlis_recurrence_scan_rows": [P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, P, I, F, P, P, I, P],
     "rlis_recurrence_scan": [P, LL, I, I, I, I, P, P, P, P, P, P, I, I, I, I, P],
     "rlis_qk_norm_store": [P, LL, I, I, I, P, P, F, P, LL, F, P, P, P, P, I, I, I, I, I, I, P, I, F, P, F, I, I, P, I, P],
     "rlis_attention_bias": [P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, I, P],
@@ -73,8 +74,8 @@ SIGNATURES = {
     "rlis_nll_rows": [P, P, P, I, I, LL, P],
     "rlis_gemm_tcgen05": [P, P, P, I, I, I, I, P],
     "rlis_gemm_tcgen05_glu": [P, P, P, I, I, I, F, F, F, P],
-    "rlis_stream_gemm_bf16": [P, P, P, I, I, I, I, I, P],
-    "rlis_stream_gemm_fused": [P, P, P, I, I, I, I, I, P, I, I, F, P, P, P, P, P],
+    "rlis_stream_gemm_bf16": [P, P, P, I, I, I, I, I, F, P],
+    "rlis_stream_gemm_fused": [P, P, P, I, I, I, I, I, P, I, I, F, P, P, P, P, F, P],
     "rlis_take_errors": [P, P],
     "rlis_stream_gemm_timeline": [I],
     "rlis_stream_gemm_timeline_read": [P, P],

@@ -21,10 +21,10 @@ class SwiGLU(FeedForward):
         self.dtype = dtype
         self.w_gate_up = None
         self.w_down = None
-        # the plain form silu(g) * u has kernels that gate inside a product; other slopes, a clipping
-        # limit or a shifted linear branch go through the gating kernel that takes them as parameters
-        self.plain = (float(getattr(spec, "slope", 1.0)) == 1.0 and getattr(spec, "limit", None) is None
-                      and float(getattr(spec, "up_shift", 0.0)) == 0.0)
+        # the form g sigmoid(slope g) * u has kernels that gate inside a product (silu at slope 1, relu at an infinite
+        # one); a clipping limit or a shifted linear branch go through the gating kernel that takes them as parameters
+        self.slope = float(getattr(spec, "slope", 1.0))
+        self.plain = getattr(spec, "limit", None) is None and float(getattr(spec, "up_shift", 0.0)) == 0.0
 
     def tensors(self) -> dict:
         s = self.spec
@@ -62,17 +62,22 @@ class SwiGLU(FeedForward):
             with span("mlp down proj"):
                 return ops.linear(act, self.w_down)
         fusable = self.dtype == torch.bfloat16 and self.interleave == 4 and self.spec.hidden % 8 == 0
-        with span("mlp gate+up, silu*up"):
+        silu = self.slope == 1.0
+        with span("mlp gate+up, silu*up" if silu else "mlp gate+up, gate*up"):
             if fusable and x.shape[0] <= ops.STREAM_GEMM_ROWS:
-                act = ops.stream_gemm(x, self.w_gate_up, swiglu4=True)       # product and gating in one kernel
+                act = ops.stream_gemm(x, self.w_gate_up, swiglu4=True, slope=self.slope)   # product and gating in one kernel
             elif fusable and x.shape[0] >= 128 and self.spec.intermediate % 128 == 0:
                 # prefill: the tcgen05 product with the gating in its epilogue (the gate|up activations
                 # never reach HBM)
-                act = ops.gemm_tcgen05(x, self.w_gate_up, "swiglu4")
+                act = ops.gemm_tcgen05(x, self.w_gate_up, "swiglu4") if silu \
+                    else ops.gemm_tcgen05(x, self.w_gate_up, "glu4", glu=(self.slope, None, 0.0))
             else:
                 gu = ops.linear(x, self.w_gate_up)
                 act = step.buffer("ffn_act", (x.shape[0], self.spec.intermediate), self.dtype)
-                ops.swiglu(gu, act, self.interleave)
+                if silu:
+                    ops.swiglu(gu, act, self.interleave)
+                else:
+                    ops.glu_act(gu, act, self.slope, None, 0.0, self.interleave)
         with span("mlp down proj"):
             return ops.linear(act, self.w_down, sink=sink)
 

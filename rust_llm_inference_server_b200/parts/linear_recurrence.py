@@ -26,6 +26,13 @@ class _Recurrence(Mixer):
         s = self.spec
         T, H = proj.shape[0], s.n_heads
         qk, hv = H * s.dim, H * s.v_dim
+        if T < ops.RECURRENCE_INPUT_PASS_TOKENS:
+            # short steps: the walk makes its inputs while it stages the tokens (one kernel)
+            o = step.buffer("recurrence_o", (T, hv), torch.float32)
+            with span("recurrence"):
+                return ops.recurrence_scan_rows(proj, self.q_off, self.k_off, self.v_off, o, state, decay, step, H, s.dim,
+                                                s.v_dim, rotation=inputs.get("rotation"), k_scale=inputs.get("k_scale", 1.0),
+                                                lower=inputs.get("lower"), gate_bias=inputs.get("gate_bias"))
         rows = step.buffer("recurrence_in", (T, 2 * qk + hv + (qk if decay is None else 0)), torch.float32)
         with span("recurrence inputs"):
             ops.recurrence_inputs(proj, self.q_off, self.k_off, self.v_off, rows, H, s.dim, s.v_dim, **inputs)

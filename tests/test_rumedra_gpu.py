@@ -120,12 +120,14 @@ WALK_SCHEDULES = {
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("portions", ["long", "short"])
 @pytest.mark.parametrize("mode", ["head_decay", "channel_decay"])
+@pytest.mark.parametrize("one_kernel", [False, True])
 @pytest.mark.parametrize("nh,d,dv,rot", [(2, 16, 24, 8), (1, 8, 16, 8), (3, 24, 16, 12), (2, 64, 32, 64), (3, 12, 20, 6),
                                          (2, 128, 128, 32), (1, 200, 40, 100), (2, 300, 16, 2)])
-def test_walk_cut_into_portions_over_slots_that_held_something_else(dtype, portions, mode, nh, d, dv, rot):
+def test_walk_cut_into_portions_over_slots_that_held_something_else(dtype, portions, mode, one_kernel, nh, d, dv, rot):
     """Six requests over three state slots that start full of junk.  Every output row against the plain recurrence over
     the whole request: with a fixed decay a head over queries and keys rotated at their positions (one head's decay is
-    1, one's close to 0), and with a forget gate a channel above a lower bound that also decides what is written."""
+    1, one's close to 0), and with a forget gate a channel above a lower bound that also decides what is written.
+    `one_kernel`: steps of fewer than 64 tokens go through the walk that makes its inputs itself."""
     from rust_llm_inference_server_b200 import ops
     rng = np.random.default_rng(d * 7 + dv)
     lens, schedule = WALK_SCHEDULES[portions]
@@ -163,7 +165,14 @@ def test_walk_cut_into_portions_over_slots_that_held_something_else(dtype, porti
         proj = dev(np.concatenate([rows[r][done[r]:done[r] + n] for r, n in entries]), dtype)
         T = st.n_tokens
         out = torch.full((T, hv), float("nan"), dtype=torch.float32, device="cuda")
-        if mode == "head_decay":
+        if one_kernel and T < ops.RECURRENCE_INPUT_PASS_TOKENS:
+            if mode == "head_decay":
+                ops.recurrence_scan_rows(proj, q_off, k_off, v_off, out, state, dev(decay), st, nh, d, dv,
+                                         rotation=(dev(freqs), rot), k_scale=0.37)
+            else:
+                ops.recurrence_scan_rows(proj, q_off, k_off, v_off, out, state, None, st, nh, d, dv, lower=dev(lower),
+                                         gate_bias=dev(gbias))
+        elif mode == "head_decay":
             buf = torch.full((T, 2 * qk + hv), float("nan"), dtype=torch.float32, device="cuda")
             ops.recurrence_inputs(proj, q_off, k_off, v_off, buf, nh, d, dv, rotation=(dev(freqs), rot), positions=st.positions,
                                   k_scale=0.37)
@@ -181,7 +190,8 @@ def test_walk_cut_into_portions_over_slots_that_held_something_else(dtype, porti
             if done[r] == lens[r]:
                 free.append(slot_of[r])
     assert done == dict(enumerate(lens)) and worst <= 2e-5, worst
-    assert ops.launches_by_kernel.get("recurrence_scan" + (".channel_decay" if mode == "channel_decay" else ""))
+    assert ops.launches_by_kernel.get(("recurrence_scan_rows" if one_kernel else "recurrence_scan") +
+                                      (".channel_decay" if mode == "channel_decay" else ""))
     ops.check_device_errors()
 
 
@@ -474,7 +484,7 @@ def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, lens
     fast = dtype == "bfloat16" and which in ("C", "E")
     for k in (("attention_bias.decode.mma", "attention_bias.prefill.mma") if fast else ("attention_bias",)) + \
             ("qk_norm_store.rot", "recurrence_inputs.rot", "recurrence_inputs.gate", "recurrence_scan",
-             "recurrence_scan.channel_decay", "head_norm_gate", "moe_route", "moe_align", "moe_combine") + \
+             "recurrence_scan.channel_decay", "recurrence_scan_rows", "recurrence_scan_rows.channel_decay", "head_norm_gate", "moe_route", "moe_align", "moe_combine") + \
             (("glu_act",) if any(l["mlp"] and l["mlp"]["kind"] == "dense" for l in U.CONFIGS[which]["layers"]) else ()):
         assert ops.launches_by_kernel.get(k), f"never launched {k}; launched {sorted(ops.launches_by_kernel)}"
     assert any(k.startswith("sum_norm") for k in ops.launches_by_kernel)
