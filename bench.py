@@ -878,16 +878,16 @@ def rumedra_config(width: int, vocab: int = 32000) -> dict:
     of 32 router outputs (28 experts of half a width and 4 identity experts, in 4 groups of which 2 are kept) beside a
     shared expert of half a width."""
     H, R = width // 64, width // 128
-    rot = {"dims": 32, "base": 1000000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    rot = {"dims": 32, "base": 500000.0, "scaling": {"factor": 16.0, "low": 1.0, "high": 8.0, "original": 8192}}
     left = {"heads": H, "kv_heads": max(1, H // 4), "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024}, "rot": rot}
     right = {"heads": R, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, R - 1)) for h in range(R)],
-             "rot": {"dims": 128, "base": 1000000.0}}
-    par = {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.5}
+             "rot": {"dims": 128, "base": 500000.0}}
+    par = {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.4}
     rec = {"heads": R, "dim": 128, "vdim": 128}
     moe = {"kind": "moe", "expert": {"ff": width // 2}, "shared": {"ff": width // 2},
            "router": {"experts": 28, "identity": 4, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
     dense = {"kind": "dense", "ff": width * 8 // 3 // 128 * 128}
-    return {"architecture": "Rumedra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 3.0},
+    return {"architecture": "Rumedra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
             "layers": [{"type": "parallel", "mixer": par, "mlp": dense}, {"type": "hgrn2", "mixer": rec, "mlp": moe},
                        {"type": "parallel", "mixer": par, "mlp": moe}, {"type": "hgrn2", "mixer": rec, "mlp": dense}]}
 

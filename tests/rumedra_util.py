@@ -57,7 +57,7 @@ CONFIGS = {
     # head on the left and of part of a head on the right; values wider and narrower than keys; two of three groups
     # kept; identity experts
     "A": model(211, 96, 1e-5, 2.0, [
-        hgrn2(3, 8, 16, moe(7, 3, 24, identity=2, groups=(3, 2), scale=1.5, shared=16)),
+        hgrn2(3, 8, 16, moe(7, 3, 24, identity=2, groups=(3, 2), scale=1.6, shared=16)),
         parallel(window_attn(4, 2, 32, 16, 0.3, 9, 16, 10000.0, (4.0, 1.0, 4.0, 64)),
                  retention(2, 16, 24, (0.9, 0.97), 8, 500.0), 0.7, 0.4, dense(40)),
         parallel(window_attn(2, 2, 16, 24, 0.5, 21, 16, 300.0), retention(3, 8, 8, (0.8, 0.95, 0.99), 8, 100.0), 1.2, 0.6),
@@ -90,13 +90,22 @@ CONFIGS = {
         hgrn2(5, 12, 20, dense(52)),
     ]),
     # wide experts and wide dense units over long prompts
-    "E": model(89, 256, 1e-5, 2.5, [
-        hgrn2(4, 32, 64, moe(3, 1, 256, identity=1, groups=(2, 1), scale=1.5, shared=128)),
-        parallel(window_attn(4, 2, 64, 64, 0.16, 130, 32, 10000.0, (8.0, 1.0, 4.0, 256)), retention(2, 64, 128, (0.97, 0.999), 64, 10000.0),
-                 0.6, 0.5, dense(256)),
+    "E": model(89, 320, 1e-5, 2.5, [
+        hgrn2(4, 16, 64, moe(3, 1, 256, identity=1, groups=(2, 1), scale=1.7, shared=128)),
+        parallel(window_attn(4, 2, 64, 64, 0.16, 130, 32, 10000.0, (6.0, 1.0, 3.0, 256)), retention(2, 64, 128, (0.97, 0.999), 64, 10000.0),
+                 0.7, 0.45, dense(384)),
+    ]),
+    # larger: one key/value head for eight query heads of 128 with values of 96, many experts in many groups, more identity
+    # experts than half the experts, a layer of each kind without a feed-forward of its own kind before it
+    "F": model(1000, 384, 1e-6, 4.0, [
+        parallel(window_attn(8, 1, 128, 96, 0.09, 64, 64, 1e6, (8.0, 1.0, 4.0, 2048)), retention(3, 96, 48, (0.9, 0.99, 0.999), 32, 1e4), 0.5, 0.5,
+                 moe(32, 6, 64, identity=0, groups=(8, 4), scale=2.0, shared=128)),
+        hgrn2(4, 48, 80, dense(512)),
+        hgrn2(2, 96, 96, moe(10, 2, 48, identity=6, groups=(4, 2), scale=1.0)),
+        parallel(window_attn(8, 1, 128, 96, 0.09, 64, 64, 1e6, (8.0, 1.0, 4.0, 2048)), retention(3, 96, 48, (0.9, 0.99, 0.999), 32, 1e4), 0.5, 0.5),
     ]),
 }
-SEEDS = {"A": 3, "B": 5, "C": 8, "D": 13, "E": 21}
+SEEDS = {"A": 3, "B": 5, "C": 8, "D": 13, "E": 21, "F": 34}
 
 
 def tensor_shapes(cfg: dict) -> dict:

@@ -21,7 +21,7 @@ def test_reader_takes_every_size_and_constant_from_the_file():
     assert (m.heads, m.dim, m.vdim) == (3, 8, 16)
     x = cfg.layers[0].mlp
     assert (x.kind, x.experts, x.top, x.ff, x.identity, x.groups, x.keep, x.scale, x.shared_ff, x.outputs) == \
-        ("moe", 7, 3, 24, 2, 3, 2, 1.5, 16, 9)
+        ("moe", 7, 3, 24, 2, 3, 2, 1.6, 16, 9)
     p = cfg.layers[1].mixer
     a, r = p.left, p.right
     assert (p.left_scale, p.right_scale) == (0.7, 0.4)

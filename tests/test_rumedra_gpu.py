@@ -449,7 +449,8 @@ def test_the_stream_after_every_layer(model_root, which):
 @pytest.mark.parametrize("which,page,lens", [("A", 16, [1, 50, 97, 200, 64, 17, 2]), ("A", 8, [130, 33, 2, 71, 40]),
                                              ("B", 16, [3, 150, 40, 2, 129, 1]), ("B", 32, [260, 31, 5, 90]),
                                              ("C", 16, [1, 70, 333, 2, 129, 64, 65]), ("C", 8, [200, 31, 5, 400]),
-                                             ("D", 16, [90, 1, 33, 150, 2]), ("E", 16, [420, 3, 200, 77])])
+                                             ("D", 16, [90, 1, 33, 150, 2]), ("E", 16, [420, 3, 200, 77]),
+                                             ("F", 16, [300, 5, 131, 64])])
 def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, lens, dtype):
     from rust_llm_inference_server_b200 import ops
     ops.launches_by_kernel.clear()
