@@ -1,6 +1,6 @@
 """The Rumedra decoder as a description: pre-norm layers over a scaled embedding, x += mixer(norm1(x)), x +=
-feed_forward(norm2(x)), with two kinds of mixer.  "hgrn2": a linear recurrence whose forget gate, bounded from
-below per channel, also decides what is written.  "parallel": two mixers side by side whose outputs are added
+feed_forward(norm2(x)), with two kinds of mixer.  "hgrn2": a linear recurrence with one gate a channel, bounded from
+below, that keeps f of the state and writes 1 - f of the new value.  "parallel": two mixers side by side whose outputs are added
 with a constant each: sliding-window grouped-query attention with biased projections, a rotate-half rotation of
 part of every head with frequencies scaled by wavelength, values of their own width and a sigmoid gate on every
 output channel; and retention, a linear recurrence with a fixed decay a head over rotated queries and keys.

@@ -1,5 +1,5 @@
 """Linear-attention recurrences over a float32 state per request: retention (a fixed decay a head, rotated
-queries and keys) and the recurrence whose forget gate also decides what is written (a decay a token and channel)."""
+queries and keys) and the recurrence with a gate a channel whose complement is the key (a decay a token and channel)."""
 
 from __future__ import annotations
 

@@ -195,7 +195,7 @@ class LightningAttentionSpec:
 
 @dataclass(frozen=True)
 class RetentionSpec:
-    """Linear attention with a fixed decay a head and no softmax or denominator: q, k = W h (n_heads x dim), rotated by
+    """A decayed outer-product state read by the query as it is (scores are neither exponentiated nor normalised), one fixed decay a head: q, k = W h (n_heads x dim), rotated by
     position where `rotation` (a rotate-half spec over the first entries of a head) is given, k times `k_scale`
     (None: dim^(-1/2)); v = W_v h (n_heads x v_dim); S_t = decay_h S_(t-1) + k_t v_t^T (float32 state per request),
     o_t = S_t^T q_t; each head's o is divided by its root mean square (times `out_norm` (v_dim,), None: no weight);
@@ -220,7 +220,7 @@ class RetentionSpec:
 
 @dataclass(frozen=True)
 class ForgetGateRecurrenceSpec:
-    """Linear attention whose forget gate also decides what is written (HGRN2): q = silu(W_q h) (n_heads x dim), v =
+    """A linear recurrence with one gate a channel that keeps f of the state and writes 1 - f of the new value (HGRN2): q = silu(W_q h) (n_heads x dim), v =
     W_v h (n_heads x v_dim), a forget gate per head and channel f = l + (1 - l) sigmoid(W_f h + f_bias) above the
     lower bound l = `lower` (n_heads * dim,); S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T (float32 state per request),
     o_t = S_t^T q_t; out = W_o (rmsnorm_per_head(o) * out_norm) with `out_norm` (v_dim,) shared by the heads."""

@@ -130,8 +130,8 @@ def window_attention(h, w, p, m, positions):
 
 
 def retention(h, w, p, m, positions, eps):
-    """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head, no softmax and no denominator; q and k
-    rotated, k times dim^(-1/2); o divided by its root mean square, gated by silu, projected."""
+    """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head (scores as they are, nothing exponentiated or
+    normalised); q and k rotated, k times dim^(-1/2); o divided by its root mean square, gated by silu, projected."""
     T = h.shape[0]
     H, d, dv = m["heads"], m["dim"], m["vdim"]
     q = rotate(linear(h, w[p + "q"]).reshape(T, H, d), positions, m["rot"])
@@ -153,7 +153,7 @@ def parallel_mixer(h, w, p, m, positions, eps):
     return float(m["left_scale"]) * left + float(m["right_scale"]) * right
 
 
-# ---- the gated recurrence whose forget gate also writes ---------------------------------------------
+# ---- the recurrence with one gate a channel that keeps f and writes 1 - f ---------------------------
 
 
 def hgrn2(h, w, p, m, eps):

@@ -126,7 +126,7 @@ WALK_SCHEDULES = {
 def test_walk_cut_into_portions_over_slots_that_held_something_else(dtype, portions, mode, one_kernel, nh, d, dv, rot):
     """Six requests over three state slots that start full of junk.  Every output row against the plain recurrence over
     the whole request: with a fixed decay a head over queries and keys rotated at their positions (one head's decay is
-    1, one's close to 0), and with a forget gate a channel above a lower bound that also decides what is written.
+    1, one's close to 0), and with a forget gate a channel above a lower bound whose complement is the key.
     `one_kernel`: steps of fewer than 64 tokens go through the walk that makes its inputs itself."""
     from rust_llm_inference_server_b200 import ops
     rng = np.random.default_rng(d * 7 + dv)
