@@ -962,7 +962,7 @@ def rumedra_kernel_rooflines(width: int, B: int, ctx: int, T: int, pk: dict, tor
             if n < ops.RECURRENCE_INPUT_PASS_TOKENS:
                 return ops.recurrence_scan_rows(proj3, 0, qk, 2 * qk, o3, state, None, st, rh, rd, rd, lower=lower, gate_bias=gb)
             ops.recurrence_inputs(proj3, 0, qk, 2 * qk, rows4, rh, rd, rd, q_silu=True, lower=lower, gate_bias=gb)
-            return ops.recurrence_scan(rows4, o3, state, None, st, rh, rd, rd)
+            return ops.recurrence_scan(rows4, o3, state, None, st, rh, rd, rd, complement_key=True)
         row(f"retention_{kind}", _graph_time_us(retention, torch), walk)
         row(f"forget_gate_recurrence_{kind}", _graph_time_us(forget_gate, torch), walk)
         us = _graph_time_us(lambda: ops.lightning_scan(proj3, 0, qk, 2 * qk, o3, state, decay, st, rh, rd, rd), torch)

@@ -39,7 +39,9 @@ struct PrepArgs {
 // E = entries of a column that one thread holds: ceil(d / 8), rounded up to a multiple of 4 so that a
 // thread reads its share of k and q from shared memory in 16-byte vectors.  Thread `slice` owns the
 // entries slice * E .. slice * E + E - 1 (those at or beyond d stay zero).
-template <typename T, int E, bool SILU, bool VEC, int PREP = 0>
+// KCOMP (with VEC): the key is the complement of the decay, k = 1 - a, taken from the staged decays: two arrays as without a
+// decay a channel, so a stage holds as many tokens.
+template <typename T, int E, bool SILU, bool VEC, int PREP = 0, bool KCOMP = false>
 __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     const T* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, float* __restrict__ out,
     float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ cu_seqlens,
@@ -47,12 +49,12 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     const PrepArgs pa) {
     pdl_wait();     // (the next kernel is let in at the end: this one runs long on few warps)
     // tokens staged at a time (shared memory holds them; a third array with a decay a channel)
-    constexpr int TOK = VEC ? (E > 16 ? 4 : 8) : (E > 8 ? 8 : 16);
+    constexpr int TOK = VEC && !KCOMP ? (E > 16 ? 4 : 8) : (E > 8 ? 8 : 16);
     constexpr int DP = SLICES * E;                 // padded d
     constexpr int ES = E + 4;                      // a thread's share sits 4 floats apart from the next one's: no bank conflicts
     constexpr int DPS = SLICES * ES;
     __shared__ __align__(16) float qs[TOK * DPS];
-    __shared__ __align__(16) float ks[TOK * DPS];
+    __shared__ __align__(16) float ks[KCOMP ? 4 : TOK * DPS];
     __shared__ __align__(16) float as[VEC ? TOK * DPS : 4];
     __shared__ float vs[TOK * COLS];
     __shared__ __align__(16) float os[TOK * COLS * SLICES];   // a column's sixteen partial sums a token
@@ -95,7 +97,7 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
             const bool ok = tt < nt && i < d;
             const T* r = proj + (size_t)(row0 + t0 + (ok ? tt : 0)) * stride + h * d + (ok ? i : 0);
             rq[j] = ok ? to_f<T>(r[q_off]) : 0.f;
-            rk[j] = ok ? to_f<T>(r[k_off]) : 0.f;
+            if (!KCOMP || PREP == 2) rk[j] = ok ? to_f<T>(r[k_off]) : 0.f;
             if (VEC && PREP != 2) ra[j] = ok ? to_f<T>(r[a_off]) : 0.f;
             if (PREP == 1) {
                 const bool turns = ok && i < pa.rot_dims;
@@ -138,12 +140,12 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
                     a = l + (1.0f - l) * (1.0f / (1.0f + expf(-z)));
                 }
                 qs[at] = silu_f(rq[j]);
-                ks[at] = ok ? 1.0f - a : 0.f;
-                as[at] = a;
+                if (!KCOMP) ks[at] = ok ? 1.0f - a : 0.f;
+                as[at] = KCOMP && !ok ? 1.0f : a;          // (an empty place keeps what it holds: a = 1, k = 0)
             } else {
                 qs[at] = SILU ? silu_f(rq[j]) : rq[j];  // silu(0) = 0 keeps the padding zero
-                ks[at] = SILU ? silu_f(rk[j]) : rk[j];
-                if (VEC) as[at] = ra[j];
+                if (!KCOMP) ks[at] = SILU ? silu_f(rk[j]) : rk[j];
+                if (VEC) as[at] = KCOMP && !(tt < nt && i < d) ? 1.0f : ra[j];
             }
         }
 #pragma unroll
@@ -156,14 +158,15 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
 #pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
             const float v = vs[tt * COLS + col];
-            const float4* kr = reinterpret_cast<const float4*>(ks + tt * DPS + slice * ES);
+            const float4* kr = reinterpret_cast<const float4*>(ks + (KCOMP ? 0 : tt * DPS + slice * ES));
             const float4* qr = reinterpret_cast<const float4*>(qs + tt * DPS + slice * ES);
             const float4* ar = reinterpret_cast<const float4*>(as + (VEC ? tt * DPS + slice * ES : 0));
             float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int e4 = 0; e4 < E / 4; ++e4) {
-                const float4 k4 = kr[e4], q4 = qr[e4];
+                const float4 q4 = qr[e4];
                 const float4 a4 = VEC ? ar[e4] : make_float4(g, g, g, g);
+                const float4 k4 = KCOMP ? make_float4(1.0f - a4.x, 1.0f - a4.y, 1.0f - a4.z, 1.0f - a4.w) : kr[e4];
                 s[4 * e4 + 0] = fmaf(a4.x, s[4 * e4 + 0], k4.x * v);
                 s[4 * e4 + 1] = fmaf(a4.y, s[4 * e4 + 1], k4.y * v);
                 s[4 * e4 + 2] = fmaf(a4.z, s[4 * e4 + 2], k4.z * v);
@@ -219,12 +222,12 @@ __global__ void silu_rows_kernel(const T* __restrict__ x, long long stride, floa
     pdl_trigger();
 }
 
-template <typename T, bool SILU, bool VEC = false, int PREP = 0>
+template <typename T, bool SILU, bool VEC = false, int PREP = 0, bool KCOMP = false>
 int launch_scan(const T* proj, long long stride, int q_off, int k_off, int v_off, float* out, float* state,
                 const float* decay, const int* cu, const int* ctx, const int* slots, dim3 grid, int nh, int d, int dv,
                 cudaStream_t stream, int a_off = 0, PrepArgs pa = PrepArgs{}) {
     const int e = (d + SLICES - 1) / SLICES;
-#define RLIS_SCAN(E) rlis_launch(lightning_scan_kernel<T, E, SILU, VEC, PREP>, grid, THREADS, 0, stream, proj, stride, q_off, k_off, \
+#define RLIS_SCAN(E) rlis_launch(lightning_scan_kernel<T, E, SILU, VEC, PREP, KCOMP>, grid, THREADS, 0, stream, proj, stride, q_off, k_off, \
                                  v_off, out, state, decay, cu, ctx, slots, nh, d, dv, a_off, pa)
     if (e <= 4) RLIS_SCAN(4);
     else if (e <= 8) RLIS_SCAN(8);
@@ -349,11 +352,12 @@ extern "C" int rlis_recurrence_inputs(const void* proj, long long stride, int q_
 }
 
 // The walk over prepared float32 rows [n_tokens, width]: q, k, v at columns q_off, k_off, v_off; a decay a head
-// (`decay` float32 [nh]) or, with `decay` null, a decay a token and channel at columns a_off.
+// (`decay` float32 [nh]) or, with `decay` null, a decay a token and channel at columns a_off; `key_is_complement`: the
+// keys are 1 - decay (what the forget gate's rows hold), and the walk takes them from the decays.
 extern "C" int rlis_recurrence_scan(const float* rows, long long width, int q_off, int k_off, int v_off, int a_off,
                                     float* out, float* state, const float* decay, const int* cu_seqlens,
                                     const int* ctx_lens, const int* state_slots, int n_seqs, int nh, int d, int dv,
-                                    cudaStream_t stream) {
+                                    int key_is_complement, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (d <= 0 || d > SLICES * MAX_E || dv <= 0 || nh <= 0 || nh > 65535) return RLIS_ERR_UNSUPPORTED;
     dim3 grid(n_seqs, nh, (dv + COLS - 1) / COLS);
@@ -361,6 +365,9 @@ extern "C" int rlis_recurrence_scan(const float* rows, long long width, int q_of
     if (decay != nullptr)
         return launch_scan<float, false, false>(rows, width, q_off, k_off, v_off, out, state, decay, cu_seqlens, ctx_lens,
                                                 state_slots, grid, nh, d, dv, stream);
+    if (key_is_complement)      // k = 1 - a: the walk takes it from the decays and does not read the rows' keys
+        return launch_scan<float, false, true, 0, true>(rows, width, q_off, k_off, v_off, out, state, nullptr, cu_seqlens,
+                                                        ctx_lens, state_slots, grid, nh, d, dv, stream, a_off);
     return launch_scan<float, false, true>(rows, width, q_off, k_off, v_off, out, state, nullptr, cu_seqlens, ctx_lens,
                                            state_slots, grid, nh, d, dv, stream, a_off);
 }
@@ -384,7 +391,7 @@ extern "C" int rlis_recurrence_scan_rows(const void* proj, long long stride, int
 #define RLIS_ROWS(T) (decay != nullptr                                                                                         \
         ? launch_scan<T, false, false, 1>((const T*)proj, stride, q_off, k_off, v_off, out, state, decay, cu_seqlens, ctx_lens,   \
                                           state_slots, grid, nh, d, dv, stream, 0, pa)                                            \
-        : launch_scan<T, false, true, 2>((const T*)proj, stride, q_off, k_off, v_off, out, state, nullptr, cu_seqlens, ctx_lens,  \
+        : launch_scan<T, false, true, 2, true>((const T*)proj, stride, q_off, k_off, v_off, out, state, nullptr, cu_seqlens, ctx_lens,  \
                                          state_slots, grid, nh, d, dv, stream, 0, pa))
     if (dtype == RLIS_F32) return RLIS_ROWS(float);
     if (dtype == RLIS_BF16) return RLIS_ROWS(bf16);

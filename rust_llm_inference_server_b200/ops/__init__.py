@@ -631,12 +631,13 @@ def recurrence_inputs(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, ou
 
 
 def recurrence_scan(rows: torch.Tensor, out: torch.Tensor, state: torch.Tensor, decay: torch.Tensor | None, step,
-                    n_heads: int, d: int, dv: int) -> torch.Tensor:
+                    n_heads: int, d: int, dv: int, complement_key: bool = False) -> torch.Tensor:
     """The linear recurrence over the step's tokens from prepared float32 rows [T, q | k | v (| a)] (see
     `recurrence_inputs`): per request and head S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t, with a_t = decay[head]
     for every channel (`decay` float32 [n_heads]) or, with `decay` None, the rows' fourth segment.  `state` float32
     [slots, nh, dv, d] holds S, transposed, between steps (a request whose first token is in this step starts from
-    zero); out float32 [T, nh dv]."""
+    zero); out float32 [T, nh dv].  `complement_key` (with a decay a channel): the rows' keys are 1 - a, as a forget
+    gate's are, and the walk takes them from the decays instead of staging them (a stage then holds twice the tokens)."""
     T, W = rows.shape
     qk, hv = n_heads * d, n_heads * dv
     _req(rows, "rows", torch.float32, (T, 2 * qk + hv + (qk if decay is None else 0)))
@@ -647,7 +648,7 @@ def recurrence_scan(rows: torch.Tensor, out: torch.Tensor, state: torch.Tensor, 
     check(lib().rlis_recurrence_scan(rows.data_ptr(), W, 0, qk, 2 * qk, 2 * qk + hv, out.data_ptr(), state.data_ptr(),
                                      decay.data_ptr() if decay is not None else None, step.cu_seqlens.data_ptr(),
                                      step.ctx_lens.data_ptr(), step.state_slots.data_ptr(), step.n_seqs, n_heads, d, dv,
-                                     _stream()), "recurrence_scan")
+                                     1 if (complement_key and decay is None) else 0, _stream()), "recurrence_scan")
     _count("recurrence_scan" + (".channel_decay" if decay is None else ""))
     return out
 

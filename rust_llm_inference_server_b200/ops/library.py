@@ -45,7 +45,7 @@ SIGNATURES = {
     "rlis_lightning_scan": [P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P, I, P],
     "rlis_recurrence_inputs": [P, LL, I, I, I, P, I, I, I, I, P, I, P, F, I, P, P, I, P],
     "rlis_recurrence_scan_rows": [P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, P, I, F, P, P, I, P],
-    "rlis_recurrence_scan": [P, LL, I, I, I, I, P, P, P, P, P, P, I, I, I, I, P],
+    "rlis_recurrence_scan": [P, LL, I, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P],
     "rlis_qk_norm_store": [P, LL, I, I, I, P, P, F, P, LL, F, P, P, P, P, I, I, I, I, I, I, P, I, F, P, F, I, I, P, I, P],
     "rlis_attention_bias": [P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, I, P],
     "rlis_attention_bias_mma_takes": [I, I],

@@ -22,7 +22,7 @@ class _Recurrence(Mixer):
         s = self.spec
         return StateSpec((s.n_heads, s.v_dim, s.dim), torch.float32)     # S transposed: a column's entries are contiguous
 
-    def _walk(self, proj, step, state, decay, **inputs):
+    def _walk(self, proj, step, state, decay, complement_key=False, **inputs):
         s = self.spec
         T, H = proj.shape[0], s.n_heads
         qk, hv = H * s.dim, H * s.v_dim
@@ -38,7 +38,7 @@ class _Recurrence(Mixer):
             ops.recurrence_inputs(proj, self.q_off, self.k_off, self.v_off, rows, H, s.dim, s.v_dim, **inputs)
         o = step.buffer("recurrence_o", (T, hv), torch.float32)
         with span("recurrence"):
-            return ops.recurrence_scan(rows, o, state, decay, step, H, s.dim, s.v_dim)
+            return ops.recurrence_scan(rows, o, state, decay, step, H, s.dim, s.v_dim, complement_key=complement_key)
 
 
 class Retention(_Recurrence):
@@ -148,7 +148,7 @@ class ForgetGateRecurrence(_Recurrence):
         T, hv = x.shape[0], s.n_heads * s.v_dim
         with span("q|f|v proj"):
             proj = ops.linear(x, self.w_in)
-        o = self._walk(proj, step, state, None, q_silu=True, lower=self.lower, gate_bias=self.f_bias)
+        o = self._walk(proj, step, state, None, complement_key=True, q_silu=True, lower=self.lower, gate_bias=self.f_bias)
         y = step.buffer("recurrence_y", (T, hv), self.dtype)
         with span("head norm"):
             ops.head_norm_gate(o, self.out_norm, self.eps, y, s.n_heads)

@@ -180,7 +180,7 @@ def test_walk_cut_into_portions_over_slots_that_held_something_else(dtype, porti
         else:
             buf = torch.full((T, 3 * qk + hv), float("nan"), dtype=torch.float32, device="cuda")
             ops.recurrence_inputs(proj, q_off, k_off, v_off, buf, nh, d, dv, q_silu=True, lower=dev(lower), gate_bias=dev(gbias))
-            ops.recurrence_scan(buf, out, state, None, st, nh, d, dv)
+            ops.recurrence_scan(buf, out, state, None, st, nh, d, dv, complement_key=nh % 2 == 0)      # either way of getting the keys
         got, at = host(out).reshape(-1, nh, dv), 0
         for r, n in entries:
             ref = want[r][done[r]:done[r] + n]
