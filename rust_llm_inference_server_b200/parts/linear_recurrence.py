@@ -22,6 +22,12 @@ class _Recurrence(Mixer):
         s = self.spec
         return StateSpec((s.n_heads, s.v_dim, s.dim), torch.float32)     # S transposed: a column's entries are contiguous
 
+    def fuses_norms(self, step) -> bool:
+        # in steps of a few rows the first product scales the rows of the norm before it and the last one adds to the
+        # stream itself (both are the streaming product)
+        s = self.spec
+        return ops.fuses_norms(step.n_tokens, self.dtype, s.hidden, s.n_heads * s.v_dim)
+
     def _walk(self, proj, step, state, decay, complement_key=False, **inputs):
         s = self.spec
         T, H = proj.shape[0], s.n_heads
@@ -91,7 +97,7 @@ class Retention(_Recurrence):
         self.out_norm = src.get(s.out_norm, "vector").contiguous() if s.out_norm is not None else None
         self.w_o = src.get(s.o_proj).contiguous()
 
-    def forward(self, x, step, cache, state, writes_cache=True):
+    def forward(self, x, step, cache, state, writes_cache=True, sink=None):
         s = self.spec
         T, hv = x.shape[0], s.n_heads * s.v_dim
         with span("q|k|v|gate proj"):
@@ -104,7 +110,7 @@ class Retention(_Recurrence):
                                gate=proj[:, self.g_off:self.g_off + hv] if s.gate_proj is not None else None,
                                activation=s.gate_act)
         with span("o proj"):
-            return ops.linear(y, self.w_o)
+            return ops.linear(y, self.w_o, sink=sink)
 
 
 class ForgetGateRecurrence(_Recurrence):
@@ -143,7 +149,7 @@ class ForgetGateRecurrence(_Recurrence):
         self.out_norm = src.get(s.out_norm, "vector").contiguous() if s.out_norm is not None else None
         self.w_o = src.get(s.o_proj).contiguous()
 
-    def forward(self, x, step, cache, state, writes_cache=True):
+    def forward(self, x, step, cache, state, writes_cache=True, sink=None):
         s = self.spec
         T, hv = x.shape[0], s.n_heads * s.v_dim
         with span("q|f|v proj"):
@@ -153,7 +159,7 @@ class ForgetGateRecurrence(_Recurrence):
         with span("head norm"):
             ops.head_norm_gate(o, self.out_norm, self.eps, y, s.n_heads)
         with span("o proj"):
-            return ops.linear(y, self.w_o)
+            return ops.linear(y, self.w_o, sink=sink)
 
 
 register_mixer("retention", Retention)
